@@ -118,29 +118,52 @@ int launch_const_decay(const float* decay, float* ab, int heads, int T, cudaStre
 // Token t: q = proj[o_q ..] + bias, rotated, -> q_out; k = proj[o_k ..] + bias: the rotated key and the value (the key before
 // rotation, or proj[o_v ..]) -> the cache row of its position: [kv_heads * dim keys | kv_heads * vdim values].
 __device__ __forceinline__ float rotated(const float* __restrict__ src, const float* __restrict__ bias, int idx, int c,
-                                         int rot_dims, const float* __restrict__ freq, float pos) {
-    const float me = src[idx] + (bias ? bias[idx] : 0.f);
+                                         int rot_dims, const float* __restrict__ freq, float pos, float sc) {
+    const float me = (src[idx] + (bias ? bias[idx] : 0.f)) * sc;
     if (c >= rot_dims) return me;
-    const int other = idx ^ 1;                 // (2i, 2i+1) pairs; a head starts on an even index when dim is even
-    const float ot = src[other] + (bias ? bias[other] : 0.f);
+    const int other = (c & 1) ? idx - 1 : idx + 1;      // (2i, 2i+1) pairs inside the head
+    const float ot = (src[other] + (bias ? bias[other] : 0.f)) * sc;
     float sn, cs;
     sincosf(pos * freq[c >> 1], &sn, &cs);
     return (c & 1) ? me * cs + ot * sn : me * cs - ot * sn;
 }
 __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
+    extern __shared__ float inv[];             // qk_norm: 1 / rms of every query head, then of every key head
     const int t = blockIdx.x;
     const float* pr = a.proj + (size_t)t * a.ldp;
     const int p = a.positions[t];
     const float pos = (float)p;
     const int nq = a.H * a.dim, nk = a.G * a.dim, nv = a.G * a.vdim;
+    if (a.qk_norm) {
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+        for (int hh = wid; hh < a.H + a.G; hh += nw) {
+            const bool isq = hh < a.H;
+            const float* src = pr + (isq ? a.o_q + hh * a.dim : a.o_k + (hh - a.H) * a.dim);
+            const float* bias = isq ? (a.q_bias ? a.q_bias + hh * a.dim : nullptr) : (a.k_bias ? a.k_bias + (hh - a.H) * a.dim : nullptr);
+            float ss = 0.f;
+            for (int d = lane; d < a.dim; d += 32) {
+                const float v = src[d] + (bias ? bias[d] : 0.f);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) inv[hh] = 1.f / sqrtf(ss / (float)a.dim + a.eps);
+        }
+        __syncthreads();
+    }
     for (int i = threadIdx.x; i < nq; i += blockDim.x)
-        a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos);
+        a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos,
+                                              a.qk_norm ? inv[i / a.dim] : 1.f);
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
     float* row = a.cache + ((size_t)pt[p >> 6] * 64 + (p & 63)) * (size_t)(nk + nv);
     for (int i = threadIdx.x; i < nk; i += blockDim.x)
-        row[i] = rotated(pr + a.o_k, a.k_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos);
-    for (int i = threadIdx.x; i < nv; i += blockDim.x)
-        row[nk + i] = a.o_v >= 0 ? pr[a.o_v + i] : pr[a.o_k + i] + (a.k_bias ? a.k_bias[i] : 0.f);
+        row[i] = rotated(pr + a.o_k, a.k_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos, a.qk_norm ? inv[a.H + i / a.dim] : 1.f);
+    const float lam = a.v_role == 2 ? a.v_mix[0] : 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        float v = a.o_v >= 0 ? pr[a.o_v + i] + (a.v_bias ? a.v_bias[i] : 0.f) : pr[a.o_k + i] + (a.k_bias ? a.k_bias[i] : 0.f);
+        if (a.v_role == 1) a.v_first[(size_t)t * nv + i] = v;
+        else if (a.v_role == 2) v = (1.f - lam) * v + lam * a.v_first[(size_t)t * nv + i];
+        row[nk + i] = v;
+    }
 }
 
 constexpr int kWinWarps = 4;
@@ -156,7 +179,8 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = a.positions[t];
     const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int n = p - lo + 1;
+    const int nf = min(a.keep_first, lo);              // kept first positions that lie before the window
+    const int n = nf + p - lo + 1;                     // key idx < nf: position idx; otherwise position lo + idx - nf
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
     const size_t rowsz = (size_t)a.G * (a.dim + a.vdim);
     for (int c = threadIdx.x; c < a.dim; c += blockDim.x) sq[c] = a.q_out[((size_t)t * a.H + h) * a.dim + c];
@@ -165,8 +189,9 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
 #pragma unroll
     for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
     for (int b0 = wid * 32; b0 < n; b0 += kWinWarps * 32) {
-        const int j = lo + b0 + lane;
-        const bool valid = j <= p;
+        const int idx = b0 + lane;
+        const int j = idx < nf ? idx : lo + idx - nf;
+        const bool valid = idx < n;
         const int jj = valid ? j : p;
         const long long base = ((long long)pt[jj >> 6] * 64 + (jj & 63)) * (long long)rowsz;
         const float* kr = a.cache + base + (size_t)g * a.dim;
@@ -182,6 +207,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
         }
         s *= a.scale;
         if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        if (a.rel) s += a.rel[(size_t)min(p - jj, a.rel_n - 1) * a.H + h];
         if (!valid) s = -INFINITY;
         const float m_new = fmaxf(m, warp_max(s));
         const float corr = expf(m - m_new);            // 0 on the first block (m = -inf)
@@ -212,6 +238,10 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     float mm = sm[0];
     for (int w = 1; w < kWinWarps; ++w) mm = fmaxf(mm, sm[w]);
     float den = 0.f;
+    if (a.sink) {
+        mm = fmaxf(mm, a.sink[h]);
+        den = expf(a.sink[h] - mm);
+    }
     for (int w = 0; w < kWinWarps; ++w) den += sl[w] * expf(sm[w] - mm);
     for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
         float num = 0.f;
@@ -269,19 +299,22 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
         for (int k = 0; k < VK; ++k)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[r][k][c] = 0.f;
-    for (int k0 = lo; k0 <= hi; k0 += WT_KEYS) {
+    const int nf = min(a.keep_first, lo);              // kept first positions before the window: a run of key tiles of their own
+    for (int seg = nf > 0 ? 0 : 1; seg < 2; ++seg) {
+    const int kend = seg ? hi + 1 : nf;
+    for (int k0 = seg ? lo : 0; k0 < kend; k0 += WT_KEYS) {
         __syncthreads();                               // the last tile's sums are done with Ks / Vs / Ps
         for (int i = tid; i < WT_KEYS * d4n; i += WT_THREADS) {
             const int c = i / d4n, d4 = i - c * d4n, key = k0 + c;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (key <= hi)
+            if (key < kend)
                 v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)g * a.dim + 4 * d4);
             *reinterpret_cast<float4*>(Ks + c * ldq + 4 * d4) = v;
         }
         for (int i = tid; i < WT_KEYS * v4n; i += WT_THREADS) {
             const int c = i / v4n, d4 = i - c * v4n, key = k0 + c;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (key <= hi)
+            if (key < kend)
                 v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)a.G * a.dim +
                                                      (size_t)g * a.vdim + 4 * d4);
             *reinterpret_cast<float4*>(Vs + c * ldv + 4 * d4) = v;
@@ -312,7 +345,8 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
                 const int key = k0 + cx + 8 * c;
                 float v = sc[i][c] * a.scale;
                 if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-                const bool vis = rv[i] && key <= pr[i] && (a.window <= 0 || key > pr[i] - a.window);
+                const bool vis = rv[i] && key < kend && key <= pr[i] && (a.window <= 0 || key > pr[i] - a.window || key < a.keep_first);
+                if (a.rel && vis) v += a.rel[(size_t)min(pr[i] - key, a.rel_n - 1) * a.H + g * grp + (2 * ry + i) % grp];
                 sc[i][c] = vis ? v : -INFINITY;
                 tmax = fmaxf(tmax, sc[i][c]);
             }
@@ -363,14 +397,25 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
             }
         }
     }
+    }
     __syncthreads();
-    if (cx == 0) { cr[2 * ry] = l[0]; cr[2 * ry + 1] = l[1]; }
+    if (cx == 0) {                                     // per row: what its sums are multiplied by at the end
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float f = 1.f / l[i];
+            if (a.sink && rv[i]) {
+                const float sk = a.sink[g * grp + (2 * ry + i) % grp], mf = fmaxf(m[i], sk), e = expf(m[i] - mf);
+                f = e / (l[i] * e + expf(sk - mf));
+            }
+            cr[2 * ry + i] = f;
+        }
+    }
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
         const int row = 8 * oy + r;
         if (row >= rows_used) continue;
-        const float inv = 1.f / cr[row];
+        const float inv = cr[row];
         float* orow = a.out + ((size_t)(row_base + row / grp) * a.H + g * grp + row % grp) * a.vdim;
 #pragma unroll
         for (int k = 0; k < VK; ++k) {
@@ -388,10 +433,13 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
 int launch_window_attention(const WindowArgs& a, int T, int n_single, const WindowTiles& tm, cudaStream_t stream) {
     FT_REQUIRE(a.H >= 1 && a.G >= 1 && a.H % a.G == 0 && a.dim >= 1 && a.vdim >= 1 && a.vdim <= 512,
                "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
-    FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0 && (a.rot_dims == 0 || (a.dim & 1) == 0),
+    FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0,
                "window attention: rotary pairs need even sizes (dim %d, rotated %d)", a.dim, a.rot_dims);
     FT_REQUIRE(a.o_v >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
-    window_write_kernel<<<T, 128, 0, stream>>>(a);
+    FT_REQUIRE(a.keep_first >= 0 && (!a.rel || a.rel_n >= 1) && (a.v_role == 0 || (a.v_first && a.o_v >= 0)) &&
+                   (a.v_role != 2 || a.v_mix),
+               "window attention: incomplete options");
+    window_write_kernel<<<T, 128, a.qk_norm ? (size_t)(a.H + a.G) * 4 : 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     const int grp = a.H / a.G;
     const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + WT_KEYS * a.vdim + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;

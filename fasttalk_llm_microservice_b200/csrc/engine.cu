@@ -172,6 +172,7 @@ struct LayeredLayer {
     // branch mixers: per branch its block in kv_cache (window attention), its S inside a state slot, and what else it keeps
     // there (the running maximum of a matrix memory, the convolution tails of a state space)
     size_t br_cache_off[2] = {0, 0}, br_s_off[2] = {0, 0}, br_x_off[2] = {0, 0};
+    size_t canon_off[2] = {0, 0};      // post-norm layers: the tails [taps - 1][width] of the two input convolutions in a slot
 };
 struct Layered {
     ft_layered_model m;
@@ -202,6 +203,10 @@ struct Layered {
     cudaStream_t side[kSide] = {};
     cudaEvent_t side_done[kSide] = {}, main_ready = nullptr;
     bool tensor = false;               // projections that tile run on the tensor cores (ft_layered_model.exact_f32 == 0)
+    // post-norm layers: the stream as every layer left it [n_layers + 1][t_max][width] (the sum over depth reads them all), the
+    // values of the first value-mixing attention layer of the step, the staging rows of latent window attention
+    float *hist = nullptr, *v_first = nullptr, *lstage = nullptr;
+    bool postnorm = false;
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
 };
@@ -700,19 +705,50 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
     cudaStream_t st = e->stream;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
     const float* fin = L.bfin;
-    if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
+    int fin_cols = c.heads * c.vdim;
+    if (c.kind == FT_BRANCH_WINDOW_ATTENTION || c.kind == FT_BRANCH_LATENT_WINDOW) {
         WindowArgs a;
-        a.proj = L.proj; a.ldp = ld; a.o_q = c.o_q; a.o_k = c.o_k; a.o_v = c.o_v;
-        a.q_bias = c.q_bias; a.k_bias = c.k_bias; a.rot_freq = c.rot_freq; a.rot_dims = c.rot_dims;
         a.q_out = L.bq; a.cache = L.kv_cache + ll.br_cache_off[k];
         a.positions = d + m.o_pos; a.seq_rows = d + m.o_rows; a.page_table = d + m.o_pt; a.max_pages = e->max_pages;
-        a.H = c.heads; a.G = c.kv_heads; a.dim = c.dim; a.vdim = c.vdim; a.window = c.window;
-        a.scale = c.scale; a.softcap = c.softcap; a.out = L.bfin;
+        a.rot_freq = c.rot_freq; a.rot_dims = c.rot_dims; a.window = c.window; a.scale = c.scale; a.softcap = c.softcap;
+        a.out = L.bfin; a.H = c.heads;
+        if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
+            a.proj = L.proj; a.ldp = ld; a.o_q = c.o_q; a.o_k = c.o_k; a.o_v = c.o_v;
+            a.q_bias = c.q_bias; a.k_bias = c.k_bias;
+            a.G = c.kv_heads; a.dim = c.dim; a.vdim = c.vdim;
+            a.qk_norm = c.qk_norm; a.eps = M.eps; a.keep_first = c.keep_first; a.sink = c.sink; a.rel = c.rel; a.rel_n = c.rel_n;
+            a.v_bias = c.v_bias; a.v_role = c.v_role; a.v_mix = c.v_mix; a.v_first = L.v_first;
+        } else {
+            // One shared key head: cached key [rotated part | normed latent], value = the latent.  The plain query part is
+            // folded through W_uk into latent space, so no per-head key or value is ever formed.
+            const int H = c.heads, R = c.rot_dims, C = c.kv_rank, D = c.dim, kd = R + C, ls = H * kd + kd + C;
+            FT_TRY(launch_rms_cols(L.proj, ld, c.o_q, c.q_norm, L.b1, c.q_rank, 0, c.q_rank, M.eps, T, st));
+            FT_TRY(dense(e, L.b1, nullptr, nullptr, c.w_uq, L.b2, T, H * (D + R), c.q_rank));
+            FT_TRY(launch_latent_stage(L.b2, H, D, R, L.proj, ld, c.o_k, C, c.kv_norm, M.eps, L.lstage, ls, T, st));
+            LinearArgs f;                   // q_lat_h = W_uk_h^T q_plain_h, beside the rotated part of head h
+            f.A = L.b2; f.lda = H * (D + R); f.a_col_stride = D + R;
+            f.W = (const __nv_bfloat16*)c.w_uk_t; f.w_stride = (long long)C * D; f.ldw = D;
+            f.C = L.lstage + R; f.ldc = ls; f.c_col_stride = kd; f.M = T; f.N = C; f.K = D; f.P = H;
+            FT_TRY(launch_linear(f, T, st));
+            launched(3);
+            a.proj = L.lstage; a.ldp = ls; a.o_q = 0; a.o_k = H * kd; a.o_v = H * kd + kd;
+            a.G = 1; a.dim = kd; a.vdim = C;
+        }
         WindowTiles tm;
         tm.tile_req = d + m.o_treq; tm.tile_q0 = d + m.o_tq0; tm.req_q_start = d + m.o_qstart; tm.req_slot = d + m.o_rslot;
         tm.req_pos0 = d + m.o_rpos0; tm.n_tiles = b.n_tiles;
         FT_TRY(launch_window_attention(a, T, b.n_decode, tm, st));
         launched(b.n_tiles > 0 && b.n_decode > 0 ? 3 : 2);
+        if (c.kind == FT_BRANCH_LATENT_WINDOW) {
+            LinearArgs v;                   // values out of latent space: o_h = W_uv_h (sum_j p_j c_j)
+            v.A = L.bfin; v.lda = c.heads * c.kv_rank; v.a_col_stride = c.kv_rank;
+            v.W = (const __nv_bfloat16*)c.w_uv; v.w_stride = (long long)c.vdim * c.kv_rank; v.ldw = c.kv_rank;
+            v.C = L.b3; v.ldc = c.heads * c.vdim; v.c_col_stride = c.vdim;
+            v.M = T; v.N = c.vdim; v.K = c.kv_rank; v.P = c.heads;
+            FT_TRY(launch_linear(v, T, st));
+            launched();
+            fin = L.b3;
+        }
     } else {
         RecurArgs r;
         r.ab = L.ab; r.o = L.bo; r.state = L.state; r.slot_stride = (long long)L.slot_stride; r.s_off = (long long)ll.br_s_off[k];
@@ -758,7 +794,7 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         FT_TRY(launch_readout(o, T, st));
         launched(2);
     }
-    return dense(e, fin, nullptr, nullptr, c.w_o, y, T, M.width, c.heads * c.vdim);
+    return dense(e, fin, nullptr, nullptr, c.w_o, y, T, M.width, fin_cols);
 }
 
 // Forward pass of a layered model.  Per layer: ONE projection of the normed input into all the parts that read it
@@ -774,14 +810,30 @@ static int forward_layered(Engine* e, const Batch& b) {
     void* hn_hi = L.tensor && T >= kTensorMinRows ? L.hn_hi : nullptr;      // planes of the normed input, written by its producer
     void* hn_lo = hn_hi ? L.hn_lo : nullptr;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
-    FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain,
-                             L.layers[0].d.form == FT_LAYER_SANDWICH ? L.layers[0].d.norm_pre1 : nullptr, st));
+    if (L.postnorm)
+        FT_TRY(launch_embed_scale(d + m.o_tokens, M.embed, M.embed_scale != 0.f ? M.embed_scale : 1.f, e->resid, L.hist, T, W, st));
+    else
+        FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain,
+                                 L.layers[0].d.form == FT_LAYER_SANDWICH ? L.layers[0].d.norm_pre1 : nullptr, st));
     launched();
+    // what a sublayer of a post-norm layer reads: the stream plus its short convolution over time
+    auto canon = [&](const LayeredLayer& ll, int which) -> int {
+        const ft_layer_desc& c = ll.d;
+        CanonArgs ca;
+        ca.x = e->resid; ca.hn = L.hn; ca.hi = hn_hi; ca.lo = hn_lo; ca.W = W;
+        ca.w = c.canon_taps >= 1 ? (which ? c.canon2 : c.canon1) : nullptr; ca.taps = c.canon_taps;
+        ca.state = L.state; ca.slot_stride = (long long)L.slot_stride; ca.tail_off = (long long)ll.canon_off[which];
+        ca.seq_rows = d + m.o_rows; ca.req_start = d + m.o_xstart; ca.req_pos0 = d + m.o_xpos0; ca.req_slot = d + m.o_xslot;
+        FT_TRY(launch_canon(ca, T, b.n_req, st));
+        launched(c.canon_taps > 1 ? 2 : 1);
+        return 0;
+    };
     for (int l = 0; l < M.n_layers; ++l) {
         const LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& c = ll.d;
         const bool sandwich = c.form == FT_LAYER_SANDWICH;
         const int ld = c.n_in;              // row stride of this layer's projection outputs
+        if (c.form == FT_LAYER_POSTNORM) FT_TRY(canon(ll, 0));
         FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_in, L.proj, T, c.n_in, W));
         const float *y0 = L.mix, *y1 = nullptr;      // the mixer's result: s0 * y0 + s1 * y1, each [T][width]
         float s0 = 1.f, s1 = 1.f;
@@ -817,24 +869,34 @@ static int forward_layered(Engine* e, const Batch& b) {
             launched(4);
             mixed = L.b3;
         } else {
-            LinearArgs a;                   // second halves of the low-rank decay and gate projections
-            a.A = L.proj + c.o_a1; a.lda = ld; a.W = (const __nv_bfloat16*)c.w_a2; a.ldw = c.rank_a;
-            a.C = L.b1; a.ldc = c.heads * c.dim; a.M = T; a.N = c.heads * c.dim; a.K = c.rank_a;
-            FT_TRY(launch_linear(a, T, st));
-            LinearArgs g;
-            g.A = L.proj + c.o_g1; g.lda = ld; g.W = (const __nv_bfloat16*)c.w_g2; g.ldw = c.rank_g;
-            g.C = L.b2; g.ldc = c.heads * c.vdim; g.M = T; g.N = c.heads * c.vdim; g.K = c.rank_g;
-            FT_TRY(launch_linear(g, T, st));
             DeltaArgs da;
+            const float* gate = L.proj + c.o_g1;
+            int ldg = ld;
+            if (c.rank_a > 0) {             // second halves of the low-rank decay and gate projections
+                LinearArgs a;
+                a.A = L.proj + c.o_a1; a.lda = ld; a.W = (const __nv_bfloat16*)c.w_a2; a.ldw = c.rank_a;
+                a.C = L.b1; a.ldc = c.heads * c.dim; a.M = T; a.N = c.heads * c.dim; a.K = c.rank_a;
+                FT_TRY(launch_linear(a, T, st));
+                da.araw = L.b1;
+            } else {                        // one decay per head and token, straight from the stacked projection
+                da.araw = L.proj + c.o_a1; da.head_decay = 1; da.ld_araw = ld;
+            }
+            if (c.rank_g > 0) {
+                LinearArgs g;
+                g.A = L.proj + c.o_g1; g.lda = ld; g.W = (const __nv_bfloat16*)c.w_g2; g.ldw = c.rank_g;
+                g.C = L.b2; g.ldc = c.heads * c.vdim; g.M = T; g.N = c.heads * c.vdim; g.K = c.rank_g;
+                FT_TRY(launch_linear(g, T, st));
+                gate = L.b2; ldg = 0;
+            }
             da.proj = L.proj; da.ldp = ld; da.o_q = c.o_q; da.o_beta = c.o_beta;
-            da.conv = c.conv_w; da.araw = L.b1; da.dt_bias = c.dt_bias; da.a_log = c.a_log;
+            da.conv = c.conv_w; da.dt_bias = c.dt_bias; da.a_log = c.a_log;
             da.qkv = L.b3; da.decay = L.b1; da.beta = L.beta; da.o = L.b4;
             da.state = L.state; da.slot_stride = (long long)L.slot_stride; da.s_off = (long long)ll.s_off;
             da.tail_off = (long long)ll.tail_off;
             da.seq_rows = d + m.o_rows; da.req_start = d + m.o_xstart; da.req_pos0 = d + m.o_xpos0;
             da.req_slot = d + m.o_xslot;
             da.heads = c.heads; da.kvh = c.kv_heads; da.dim = c.dim; da.vdim = c.vdim; da.taps = c.conv;
-            FT_TRY(launch_delta(da, L.b2, c.out_norm, M.eps, T, b.n_req, st));
+            FT_TRY(launch_delta(da, gate, c.out_norm, M.eps, T, b.n_req, st, ldg, c.gate_act));
             launched(6);
             mixed = L.b4;
         }
@@ -844,7 +906,27 @@ static int forward_layered(Engine* e, const Batch& b) {
         // gains of the norm that the next layer (or the head) reads: one number, or one per coordinate
         const float gain_next = nx ? nx->norm_gain : M.final_norm_gain;
         const float* gain_next_w = nx ? (nx->form == FT_LAYER_SANDWICH ? nx->norm_pre1 : nullptr) : M.final_norm_w;
-        if (sandwich) {
+        if (c.form == FT_LAYER_POSTNORM) {
+            // x += norm(mixer);  x += norm(ff(x + conv(x)));  the layer's result joins the depth history and the stream that
+            // goes on is the weighted sum over it
+            const bool has_ff = c.ff_kind != FT_FF_NONE;
+            PostNormArgs pa;
+            pa.x = e->resid; pa.W = W; pa.eps = M.eps; pa.y0 = y0; pa.y1 = y1; pa.s0 = s0; pa.s1 = s1; pa.post_w = c.norm_post1;
+            if (c.mixer == FT_MIXER_BRANCHES) { pa.b0 = c.branch[0].o_bias; pa.b1 = y1 ? c.branch[1].o_bias : nullptr; }
+            auto ends_layer = [&](PostNormArgs& p) { p.hist = L.hist; p.depth_w = c.depth_w; p.k = l + 1; p.t_stride = e->t_max; };
+            if (!has_ff) ends_layer(pa);
+            FT_TRY(launch_postnorm(pa, T, st));
+            launched();
+            if (has_ff) {
+                FT_TRY(canon(ll, 1));
+                FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_gu, c.w_down, c.ff, c.ff_act, L.mix, T));
+                PostNormArgs pf;
+                pf.x = e->resid; pf.W = W; pf.eps = M.eps; pf.y0 = L.mix; pf.post_w = c.norm_post2;
+                ends_layer(pf);
+                FT_TRY(launch_postnorm(pf, T, st));
+                launched();
+            }
+        } else if (sandwich) {
             FT_REQUIRE(gain_next_w, "engine: layer %d: a sandwich layer needs per-coordinate gains in what follows it", l);
             SandwichArgs sa;
             sa.x = e->resid; sa.hn = L.hn; sa.hi = hn_hi; sa.lo = hn_lo; sa.W = W; sa.eps = M.eps;
@@ -889,7 +971,13 @@ static int forward_layered(Engine* e, const Batch& b) {
             FT_CHECK_CUDA(cudaMemcpyAsync(L.trail + (size_t)l * e->t_max * W, e->resid, (size_t)T * W * 4,
                                           cudaMemcpyDeviceToDevice, st));
     }
-    if (b.n_logit_rows > 0) {
+    if (b.n_logit_rows > 0 && L.postnorm) {
+        // the model's norm over the wanted rows only, then the head
+        FT_TRY(launch_rms_rows(e->resid, b.logit_rows_identity ? nullptr : d + m.o_lrow, M.final_norm_w, M.final_norm_gain, L.xlast,
+                               b.n_logit_rows, W, M.eps, st));
+        launched();
+        FT_TRY(dense(e, L.xlast, nullptr, nullptr, M.head, e->logits, b.n_logit_rows, M.vocab, W, M.logit_softcap));
+    } else if (b.n_logit_rows > 0) {
         const float* x = L.hn;
         if (!b.logit_rows_identity) {
             FT_TRY(launch_gather_rows(L.hn, d + m.o_lrow, L.xlast, b.n_logit_rows, W, st));
@@ -1404,16 +1492,35 @@ static int engine_init_layered(Engine* e) {
     size_t cache_floats = 0, buf = 1, act_cols = 1;
     size_t kv_floats = 0, br_q = 0, br_v = 0, br_o = 0, br_fin = 0, br_heads = 0, e_max_s = 1;
     int n_in_max = 1, top_max = 1, heads_max = 1, rank_max = 0;
+    size_t vfirst_cols = 0, lstage_cols = 0;
+    bool use_hist = false;
     for (int l = 0; l < M.n_layers; ++l) {
         LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& d = ll.d;
         FT_REQUIRE(d.n_in >= 1 && d.w_in, "engine: layer %d is incomplete", l);
         const bool sandwich = d.form == FT_LAYER_SANDWICH;
-        if (sandwich) {
+        const bool post = d.form == FT_LAYER_POSTNORM;
+        FT_REQUIRE(post == (L.layers[0].d.form == FT_LAYER_POSTNORM), "engine: post-norm layers do not mix with other layer forms");
+        if (post) {
+            FT_REQUIRE(d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.ff_kind == FT_FF_DENSE && d.norm_post2)),
+                       "engine: post-norm layer %d lacks norm gains (its feed-forward is dense or absent)", l);
+            FT_REQUIRE(d.canon_taps >= 0 && d.canon_taps <= 17 && (d.canon_taps == 0 || (d.canon1 && (d.ff_kind == FT_FF_NONE || d.canon2))),
+                       "engine: post-norm layer %d: bad input convolutions", l);
+            L.postnorm = true;
+            if (d.canon_taps > 1) {
+                for (int k = 0; k < (d.ff_kind == FT_FF_NONE ? 1 : 2); ++k) {
+                    ll.canon_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)(d.canon_taps - 1) * M.width;
+                }
+                L.slot_stride = (L.slot_stride + 3) & ~size_t(3);
+                L.n_stateful++;
+            }
+            if (d.depth_w) use_hist = true;
+        } else if (sandwich) {
             FT_REQUIRE(d.norm_pre1 && d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.norm_pre2 && d.norm_post2)),
                        "engine: sandwich layer %d lacks norm gains", l);
         } else {
-            FT_REQUIRE(d.form == FT_LAYER_GATED && d.rg_bias && d.o_rg1 >= 0 && d.mixer != FT_MIXER_BRANCHES,
+            FT_REQUIRE(d.form == FT_LAYER_GATED && d.rg_bias && d.o_rg1 >= 0 && d.mixer != FT_MIXER_BRANCHES && d.rank_a >= 1 && d.rank_g >= 1,
                        "engine: gated layer %d is incomplete (it takes latent attention or channel delta)", l);
         }
         n_in_max = std::max(n_in_max, d.n_in);
@@ -1434,9 +1541,28 @@ static int engine_init_layered(Engine* e) {
                 br_fin = std::max(br_fin, hv);
                 if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
                     FT_REQUIRE(c.window >= 0 && (c.rot_dims == 0 || c.rot_freq), "engine: layer %d branch %d: bad window or rotation", l, k);
+                    FT_REQUIRE(c.keep_first >= 0 && (!c.rel || c.rel_n >= 1) && (c.v_role == 0 || c.o_v >= 0) && (c.v_role != 2 || c.v_mix),
+                               "engine: layer %d branch %d: incomplete attention options", l, k);
                     ll.br_cache_off[k] = kv_floats;
                     kv_floats += (size_t)e->cfg.num_pages * kKvTile * c.kv_heads * (c.dim + c.vdim);
                     br_q = std::max(br_q, (size_t)c.heads * c.dim);
+                    if (c.v_role) {
+                        FT_REQUIRE(vfirst_cols == 0 || vfirst_cols == (size_t)c.kv_heads * c.vdim,
+                                   "engine: layer %d: value mixing needs the value sizes of its first layer", l);
+                        FT_REQUIRE(c.v_role == 1 || vfirst_cols, "engine: layer %d mixes values before any layer kept them", l);
+                        vfirst_cols = (size_t)c.kv_heads * c.vdim;
+                    }
+                } else if (c.kind == FT_BRANCH_LATENT_WINDOW) {
+                    FT_REQUIRE(c.window >= 0 && c.kv_rank >= 1 && c.q_rank >= 1 && c.rot_dims >= 0 && (c.rot_dims == 0 || c.rot_freq) &&
+                                   c.w_uq && c.w_uk_t && c.w_uv && c.q_norm && c.kv_norm,
+                               "engine: latent-window layer %d branch %d is incomplete", l, k);
+                    const size_t kd = (size_t)c.rot_dims + c.kv_rank;
+                    ll.br_cache_off[k] = kv_floats;
+                    kv_floats += (size_t)e->cfg.num_pages * kKvTile * (kd + c.kv_rank);
+                    br_q = std::max(br_q, (size_t)c.heads * kd);
+                    br_fin = std::max(br_fin, (size_t)c.heads * c.kv_rank);
+                    lstage_cols = std::max(lstage_cols, (size_t)c.heads * kd + kd + c.kv_rank);
+                    buf = std::max(buf, std::max((size_t)c.q_rank, (size_t)c.heads * (c.dim + c.rot_dims)));
                 } else if (c.kind == FT_BRANCH_DECAY_ATTENTION) {
                     FT_REQUIRE(c.kv_heads == c.heads && c.decay && c.out_norm && c.o_v >= 0 && c.o_g >= 0 &&
                                    c.o_k == c.o_q + c.heads * c.dim && c.o_v == c.o_k + c.heads * c.dim,
@@ -1482,9 +1608,9 @@ static int engine_init_layered(Engine* e) {
             buf = std::max(buf, (size_t)d.heads * d.kv_rank);
             rank_max = std::max(rank_max, d.kv_rank);
         } else if (d.mixer == FT_MIXER_CHANNEL_DELTA) {
-            FT_REQUIRE(d.kv_heads >= 1 && d.heads % d.kv_heads == 0 && d.conv >= 1 && d.rank_a >= 1 && d.rank_g >= 1 &&
-                           d.conv_w && d.w_a2 && d.w_g2 && d.dt_bias && d.a_log && d.out_norm && d.o_q >= 0 &&
-                           d.o_beta >= 0 && d.o_a1 >= 0 && d.o_g1 >= 0,
+            FT_REQUIRE(d.kv_heads >= 1 && d.heads % d.kv_heads == 0 && d.conv >= 1 && d.rank_a >= 0 && d.rank_g >= 0 &&
+                           d.conv_w && (d.rank_a == 0 || d.w_a2) && (d.rank_g == 0 || d.w_g2) && d.dt_bias && d.a_log && d.out_norm &&
+                           d.o_q >= 0 && d.o_beta >= 0 && d.o_a1 >= 0 && d.o_g1 >= 0,
                        "engine: channel-delta layer %d is incomplete", l);
             const size_t ch = (size_t)2 * d.kv_heads * d.dim + (size_t)d.heads * d.vdim;
             ll.s_off = L.slot_stride;
@@ -1508,7 +1634,7 @@ static int engine_init_layered(Engine* e) {
             FT_REQUIRE(d.router_rows == 0 || d.router_rows >= d.experts, "engine: layer %d: router_rows below the expert count", l);
             e_max_s = std::max(e_max_s, (size_t)std::max(d.experts, d.router_rows));
         } else if (d.ff_kind == FT_FF_DENSE) {
-            FT_REQUIRE(sandwich && d.ff >= 1 && d.w_gu && d.w_down, "engine: dense feed-forward layer %d is incomplete", l);
+            FT_REQUIRE((sandwich || post) && d.ff >= 1 && d.w_gu && d.w_down, "engine: dense feed-forward layer %d is incomplete", l);
             act_cols = std::max(act_cols, (size_t)d.ff);
         } else {
             FT_REQUIRE(d.ff_kind == FT_FF_NONE, "engine: layer %d has an unknown feed-forward %d", l, d.ff_kind);
@@ -1540,6 +1666,9 @@ static int engine_init_layered(Engine* e) {
         FT_TRY(alloc(&L.mix2, T * W * 4));
         buf = std::max(buf, br_fin);               // the planes of an output projection's input
     }
+    if (use_hist) FT_TRY(alloc(&L.hist, (size_t)(M.n_layers + 1) * T * W * 4));
+    if (vfirst_cols) FT_TRY(alloc(&L.v_first, T * vfirst_cols * 4));
+    if (lstage_cols) FT_TRY(alloc(&L.lstage, T * lstage_cols * 4));
     FT_TRY(alloc(&L.ffa, T * act_cols * 2 * 4));
     FT_TRY(alloc(&L.ffb, T * act_cols * 4));
     FT_TRY(alloc(&L.rlog, T * e_max_s * 4));
@@ -1611,6 +1740,7 @@ static void engine_free(Engine* e) {
         cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.kv_cache); cudaFree(L.bq); cudaFree(L.bv); cudaFree(L.bo); cudaFree(L.bfin); cudaFree(L.ab); cudaFree(L.gates);
+        cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage);
         cudaFree(L.floor); cudaFree(L.mix2); cudaFree(L.ffa); cudaFree(L.ffb); cudaFree(L.rlog);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);

@@ -155,10 +155,13 @@ struct DeltaArgs {
     const int* req_pos0 = nullptr;    // [n_req] position of that row in its sequence
     const int* req_slot = nullptr;    // [n_req] state slot
     int heads = 0, kvh = 0, dim = 0, vdim = 0, taps = 0;
+    int head_decay = 0;               // 1: araw holds one value per head (row stride ld_araw), dt_bias is [heads]
+    int ld_araw = 0;
 };
 // prep (convolutions, norms, decays) -> tails -> recurrence -> output norm and gate (in place in a.o)
+// gate rows have stride ldg (0: heads * vdim); gate_act 0: sigmoid, 1: silu
 int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, float eps, int T, int n_req,
-                 cudaStream_t stream);
+                 cudaStream_t stream, int ldg = 0, int gate_act = 0);
 int launch_route(const float* proj, int ldp, int o_router, int E, int top, int groups, int keep, int* ids, float* wts,
                  int* seg, int* slot_token, int* slot_pos, int T, cudaStream_t stream, int route_kind = FT_ROUTE_SOFTMAX,
                  int normalise = 0, float scale = 1.f);
@@ -199,6 +202,17 @@ struct WindowArgs {
     int H = 0, G = 0, dim = 0, vdim = 0, window = 0;
     float scale = 1.f, softcap = 0.f;
     float* out = nullptr;                         // [T][H * vdim]
+    // options, off by default
+    int qk_norm = 0;                              // q and k divided by their root mean square per head (before rotation)
+    float eps = 0.f;
+    int keep_first = 0;                           // positions below this stay visible beyond the window
+    const float* sink = nullptr;                  // [H]: exp(sink) joins the softmax denominator
+    const float* rel = nullptr;                   // [rel_n][H]: bias by distance, the last row for every larger distance
+    int rel_n = 0;
+    const float* v_bias = nullptr;                // [G * vdim]
+    int v_role = 0;                               // 1: values also go to v_first; 2: v <- (1 - v_mix) v + v_mix v_first
+    const float* v_mix = nullptr;                 // [1]
+    float* v_first = nullptr;                     // [T][G * vdim] of the step
 };
 // The step's prompt portions as the batch builder lists them: 64-token query tiles (request, first token), and per request
 // its first row in the step, its page-table row and the position of its first token.
@@ -270,6 +284,51 @@ struct ReadoutArgs {
     float* out = nullptr;                         // [T][heads * vdim]
 };
 int launch_readout(const ReadoutArgs& a, int T, cudaStream_t stream);
+
+// ---- postnorm.cu (FT_LAYER_POSTNORM: input convolutions, normed sublayer results, the weighted sum over depth; and the
+// staging of latent window attention)
+// x[t] = embed[token] * scale; the same row into hist (X_0) when given
+int launch_embed_scale(const int* tokens, const void* embed, float scale, float* x, float* hist, int T, int W, cudaStream_t stream);
+// What a sublayer reads: hn[t] = x[t] + sum_j w[:, j] x[t - taps + 1 + j] over the rows of t's own sequence; rows before the
+// step come from the slot's tail [taps - 1][W] at tail_off (zeros before position 0).  hi / lo (may be null): hn as planes.
+// w null: hn = x.  Afterwards the tail takes the sequence's last taps - 1 rows.
+struct CanonArgs {
+    const float* x = nullptr;
+    float* hn = nullptr;
+    void *hi = nullptr, *lo = nullptr;
+    const float* w = nullptr;                     // [W][taps]
+    int taps = 0, W = 0;
+    float* state = nullptr;
+    long long slot_stride = 0, tail_off = 0;
+    const int *seq_rows = nullptr, *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+};
+int launch_canon(const CanonArgs& a, int T, int n_req, cudaStream_t stream);
+// x += rms(y0 + b0 [+ y1 + b1]) * post_w.  With hist: the new row is X_k (written to hist[k]) and the stream becomes
+// sum_{j <= k} depth_w[j] hist[j]; hist is [n][t_stride][W].
+struct PostNormArgs {
+    float* x = nullptr;
+    const float *y0 = nullptr, *y1 = nullptr, *b0 = nullptr, *b1 = nullptr;
+    float s0 = 1.f, s1 = 1.f;
+    const float* post_w = nullptr;
+    float* hist = nullptr;
+    const float* depth_w = nullptr;
+    int k = 0;
+    long long t_stride = 0;
+    int W = 0;
+    float eps = 0.f;
+};
+int launch_postnorm(const PostNormArgs& a, int T, cudaStream_t stream);
+// out[i] = rms(x[rows ? rows[i] : i]) * w (gain per coordinate) or * gain
+int launch_rms_rows(const float* x, const int* rows, const float* w, float gain, float* out, int n, int W, float eps,
+                    cudaStream_t stream);
+// dst[t][dst_off + c] = rms(src[t][src_off .. + n)) * w[c]: a run of columns normed to a place (rows of stride lds / ldd)
+int launch_rms_cols(const float* src, int lds, int src_off, const float* w, float* dst, int ldd, int dst_off, int n, float eps,
+                    int T, cudaStream_t stream);
+// Latent window attention: the staging row [heads x (rot query part | room for the folded plain query)] [rot key part |
+// normed latent] [normed latent] of every token, from the query projection q [T][heads][dim | rot] and the layer's projection
+// (rank latent columns, then rot columns, at o_k; latent gain w)
+int launch_latent_stage(const float* q, int heads, int dim, int rot, const float* proj, int ldp, int o_k, int rank, const float* w,
+                        float eps, float* stage, int lds, int T, cudaStream_t stream);
 
 // ---- sampling.cu
 int launch_sample(const float* logits, int B, int V, const float* temperature, const int* top_k,

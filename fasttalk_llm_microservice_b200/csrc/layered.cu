@@ -881,7 +881,9 @@ delta_prep_kernel(DeltaArgs a) {
     for (int c = 2 * qk + threadIdx.x; c < ch; c += blockDim.x) dst[c] = sh[c];
     const int hd = a.heads * a.dim;
     for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-        const float z = a.araw[(size_t)t * hd + i] + a.dt_bias[i];
+        // one decay per head and key channel, or (head_decay) one per head, written to all of the head's channels
+        const float z = a.head_decay ? a.araw[(size_t)t * a.ld_araw + i / a.dim] + a.dt_bias[i / a.dim]
+                                     : a.araw[(size_t)t * hd + i] + a.dt_bias[i];
         const float sp = z > 20.f ? z : log1pf(expf(z));
         a.decay[(size_t)t * hd + i] = expf(-expf(a.a_log[i / a.dim]) * sp);
     }
@@ -1022,23 +1024,24 @@ delta_rule_kernel(DeltaArgs a) {
     }
 }
 
-// o[t, h, :] <- o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :]), one warp per (token, head)
+// o[t, h, :] <- o / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]), one warp per (token, head); act = sigmoid or silu;
+// gate rows have stride ldg
 __global__ void __launch_bounds__(128)
 delta_out_kernel(float* __restrict__ o, const float* __restrict__ gate, const float* __restrict__ w, int vdim, float eps,
-                 int n_pairs) {
+                 int n_pairs, int heads, int ldg, int gate_act) {
     const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (pair >= n_pairs) return;
     float* p = o + (size_t)pair * vdim;
-    const float* g = gate + (size_t)pair * vdim;
+    const float* g = gate + (size_t)(pair / heads) * ldg + (size_t)(pair % heads) * vdim;
     float ss = 0.f;
     for (int c = lane; c < vdim; c += 32) ss += p[c] * p[c];
     ss = warp_sum(ss);
     const float r = 1.f / sqrtf(ss / (float)vdim + eps);
-    for (int c = lane; c < vdim; c += 32) p[c] = p[c] * r * w[c] * sigmoid_exact(g[c]);
+    for (int c = lane; c < vdim; c += 32) p[c] = p[c] * r * w[c] * sigmoid_exact(g[c]) * (gate_act == 1 ? g[c] : 1.f);
 }
 
 int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, float eps, int T, int n_req,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, int ldg, int gate_act) {
     const int ch = 2 * a.kvh * a.dim + a.heads * a.vdim;
     FT_REQUIRE(a.taps >= 1 && a.taps <= 17, "channel delta: %d convolution taps are beyond 17", a.taps);
     FT_REQUIRE(a.dim <= 256 && a.vdim <= 256, "channel delta: head sizes %d / %d are beyond 256", a.dim, a.vdim);
@@ -1078,7 +1081,8 @@ int launch_delta(const DeltaArgs& a, const float* gate, const float* out_norm, f
 #undef FT_DELTA_ONE
     FT_CHECK_CUDA(cudaGetLastError());
     const int n_pairs = T * a.heads;
-    delta_out_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(a.o, gate, out_norm, a.vdim, eps, n_pairs);
+    delta_out_kernel<<<(n_pairs + 3) / 4, 128, 0, stream>>>(a.o, gate, out_norm, a.vdim, eps, n_pairs, a.heads,
+                                                            ldg > 0 ? ldg : a.heads * a.vdim, gate_act);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -11,6 +11,14 @@ weight stored as gain - 1), branch mixers — a gated matrix memory ("mlstm"), a
 linear attention with a constant decay per head — and a feed-forward that is either a dense SwiGLU or a mixture of
 squared-ReLU experts with sigmoid scores and a shared expert.  Its mixers are ft_branch_desc entries of the native engine.
 
+The third design is Vonedra: post-norm layers (the sublayers read the stream itself through a short causal convolution over
+time, only their results are RMS-normed, and the stream that goes on is a learned weighted sum of what every earlier layer
+left), three mixers — grouped-query attention with unit-RMS queries and keys, a bias by bucketed distance, a window that
+keeps the first tokens, a sink in the softmax and values mixed with those of the first such layer; latent attention with a
+query latent, a shared rotated key part and a window (one shared key head in the engine: FT_BRANCH_LATENT_WINDOW); a gated
+delta rule with one decay per head and token and a SiLU gate (the channel-delta kernels with the decay written to all of a
+head's channels) — and a dense SwiGLU feed-forward.
+
 The reference names models by tag only and owns no model code (app/utils/config.py:86, docker-compose.vllm.yml:39); this
 module is the model side of what its engine container would load: config.json -> LayeredSpec, model.safetensors -> the
 tensors by their names in the file, pack() -> the device arrays and descriptors the native engine reads.
@@ -27,14 +35,15 @@ import torch
 
 MIXER_LATENT_ATTENTION, MIXER_CHANNEL_DELTA, MIXER_BRANCHES = 1, 2, 3
 FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
-LAYER_GATED, LAYER_SANDWICH = 0, 1
+LAYER_GATED, LAYER_SANDWICH, LAYER_POSTNORM = 0, 1, 2
 ACT_SWIGLU, ACT_RELU2 = 0, 1
 ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
-BRANCH_WINDOW_ATTENTION, BRANCH_DECAY_ATTENTION, BRANCH_MATRIX_MEMORY, BRANCH_STATE_SPACE = 1, 2, 3, 4
+BRANCH_WINDOW_ATTENTION, BRANCH_DECAY_ATTENTION, BRANCH_MATRIX_MEMORY, BRANCH_STATE_SPACE, BRANCH_LATENT_WINDOW = 1, 2, 3, 4, 5
 MIXERS = {"latent_attention": MIXER_LATENT_ATTENTION, "channel_delta": MIXER_CHANNEL_DELTA,
           "mlstm": MIXER_BRANCHES, "mamba2": MIXER_BRANCHES, "parallel": MIXER_BRANCHES}
 BRANCHES = {"window_attention": BRANCH_WINDOW_ATTENTION, "decay_attention": BRANCH_DECAY_ATTENTION,
-            "matrix_memory": BRANCH_MATRIX_MEMORY, "state_space": BRANCH_STATE_SPACE}
+            "matrix_memory": BRANCH_MATRIX_MEMORY, "state_space": BRANCH_STATE_SPACE, "latent_window": BRANCH_LATENT_WINDOW}
+POSTNORM_MIXERS = ("attention", "latent_attention", "delta")      # Vonedra's names for its mixers
 SANDWICH_MIXERS = ("mlstm", "mamba2", "parallel")
 
 
@@ -57,6 +66,17 @@ class BranchSpec:
     gate_cap: float = 0.0           # matrix memory
     conv: int = 0                   # state space
     norm_groups: int = 1
+    # window attention options (Vonedra's attention)
+    qk_norm: bool = False
+    keep_first: int = 0
+    rel_rows: int = 0               # rows of the distance-bias table (0 = none)
+    rel_far: float = 0.0            # distance from which the last row applies
+    sink: bool = False
+    biases: bool = False            # q, k, v and output biases
+    v_mix: bool = False
+    # latent window attention: dim = plain query/key size per head, rot_dims = rotated size
+    kv_rank: int = 0
+    q_rank: int = 0
 
 
 @dataclass(frozen=True)
@@ -77,7 +97,7 @@ class LayerSpec:
     groups: int = 1
     keep: int = 1
     # sandwich layers (Gedelorn)
-    form: str = "gated"             # "gated" | "sandwich"
+    form: str = "gated"             # "gated" | "sandwich" | "postnorm"
     branches: Tuple[BranchSpec, ...] = ()
     ff_kind: str = ""               # sandwich: "" (none) | "dense" | "moe"
     route_scale: float = 1.0
@@ -93,6 +113,8 @@ class LayeredSpec:
     eps: float
     logit_softcap: float
     layers: Tuple[LayerSpec, ...] = field(default_factory=tuple)
+    embed_scale: float = 1.0        # post-norm models
+    canon_taps: int = 0             # post-norm models: taps of the input convolutions
 
     # the attributes the serving code reads from any model spec
     @property
@@ -105,6 +127,9 @@ class LayeredSpec:
         for l in self.layers:
             if l.form == "sandwich":
                 out.append(_sandwich_layer_config(l))
+                continue
+            if l.form == "postnorm":
+                out.append(_postnorm_layer_config(l))
                 continue
             if l.mixer == "latent_attention":
                 mixer = {"dim": l.dim, "heads": l.heads, "kv_rank": l.kv_rank, "scale": l.scale, "vdim": l.vdim}
@@ -119,7 +144,71 @@ class LayeredSpec:
                "width": self.width}
         if self.logit_softcap or self.architecture == "Gitozen":
             cfg["logit_softcap"] = self.logit_softcap
+        if self.layers and self.layers[0].form == "postnorm":
+            cfg["canon"] = {"taps": self.canon_taps}
+            cfg["embedding"] = {"scale": self.embed_scale}
         return cfg
+
+
+def _postnorm_layer_config(l: LayerSpec) -> Dict:
+    if l.mixer == "delta":
+        mixer = {"conv": l.conv, "dim": l.dim, "heads": l.heads, "kv_heads": l.kv_heads, "vdim": l.vdim}
+    else:
+        b = l.branches[0]
+        if l.mixer == "attention":
+            mixer = {"bias_max": b.rel_far, "dim": b.dim, "heads": b.heads, "kv_heads": b.kv_heads,
+                     "mask": {"keep_first": b.keep_first, "size": b.window}, "scale": b.scale, "v_mix": b.v_mix, "vdim": b.vdim}
+        else:
+            mixer = {"dim": b.dim, "heads": b.heads, "kv_rank": b.kv_rank, "mask": {"size": b.window}, "q_rank": b.q_rank,
+                     "rot": {"base": b.rot_base, "dims": b.rot_dims}, "rot_dim": b.rot_dims, "scale": b.scale, "vdim": b.vdim}
+    return {"mixer": mixer, "mlp": {"ff": l.ff, "kind": "dense"} if l.ff_kind == "dense" else None, "type": l.mixer}
+
+
+def _postnorm_layer_from_config(i: int, l: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]]) -> LayerSpec:
+    kind, m = l["type"], l["mixer"]
+    kw = dict(mixer=kind, form="postnorm")
+    if kind == "attention":
+        mask = m.get("mask") or {}
+        rows = int(shapes[f"l{i}.mix.rel"][0]) if shapes is not None else int(m.get("bias_rows", 0))
+        kw["branches"] = (BranchSpec(
+            kind="window_attention", heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+            vdim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]), window=int(mask.get("size", 0)),
+            keep_first=int(mask.get("keep_first", 0)), qk_norm=True, rel_rows=rows, rel_far=float(m.get("bias_max", 0.0)),
+            sink=True, biases=True, v_mix=bool(m.get("v_mix", False))),)
+    elif kind == "latent_attention":
+        rot = m.get("rot") or {}
+        rd = int(m.get("rot_dim", rot.get("dims", 0)))
+        if rd and int(rot.get("dims", rd)) != rd:
+            raise ValueError(f"layer {i}: the rotated key part has {rd} coordinates, the rotation covers {rot.get('dims')}")
+        kw["branches"] = (BranchSpec(
+            kind="latent_window", heads=int(m["heads"]), kv_heads=1, dim=int(m["dim"]), vdim=int(m["vdim"]),
+            scale=float(m["scale"]), window=int((m.get("mask") or {}).get("size", 0)), rot_dims=rd,
+            rot_base=float(rot.get("base", 10000.0)), kv_rank=int(m["kv_rank"]),
+            q_rank=int(shapes[f"l{i}.mix.dq"][0]) if shapes is not None else int(m["q_rank"])),)
+    elif kind == "delta":
+        kw.update(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                  conv=int(m["conv"]))
+    else:
+        raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+    mlp = l.get("mlp")
+    if mlp:
+        if mlp.get("kind") != "dense":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        kw.update(ff_kind="dense", ff=int(mlp["ff"]))
+    return LayerSpec(**kw)
+
+
+def distance_rows(rows: int, far: float) -> List[int]:
+    """Row of a distance-bias table with `rows` rows for every distance 0 .. ceil(far): one row per distance below rows // 2,
+    then equal steps of log(distance) up to `far`, from where the last row applies."""
+    import math
+    half = rows // 2
+    if not far > half >= 1:
+        raise ValueError(f"a distance-bias table of {rows} rows needs a far distance above {half} (got {far})")
+    out = []
+    for n in range(int(math.ceil(far)) + 1):
+        out.append(n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
 
 
 def _branch_config(b: BranchSpec) -> Dict:
@@ -206,8 +295,12 @@ def _sandwich_layer_from_config(i: int, l: Dict) -> LayerSpec:
 def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None, name: str = "checkpoint") -> LayeredSpec:
     """config.json (+ tensor shapes, for the sizes only a shape gives) -> LayeredSpec."""
     layers = []
+    postnorm = cfg.get("architecture") == "Vonedra"
     for i, l in enumerate(cfg["layers"]):
         kind, m = l["type"], l["mixer"]
+        if postnorm:
+            layers.append(_postnorm_layer_from_config(i, l, shapes))
+            continue
         if kind not in MIXERS:
             raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
         if kind in SANDWICH_MIXERS:
@@ -234,7 +327,8 @@ def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = N
     cap = cfg.get("logit_softcap")
     return LayeredSpec(name=name, architecture=str(cfg.get("architecture", "Gitozen")), width=int(cfg["width"]),
                        vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), logit_softcap=float(cap) if cap else 0.0,
-                       layers=tuple(layers))
+                       layers=tuple(layers), embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
+                       canon_taps=int((cfg.get("canon") or {}).get("taps", 0)))
 
 
 def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
@@ -245,6 +339,9 @@ def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
         p = f"l{i}."
         if l.form == "sandwich":
             out.update(_sandwich_shapes(p, l, W))
+            continue
+        if l.form == "postnorm":
+            out.update(_postnorm_shapes(p, i, l, W, spec.canon_taps))
             continue
         out[p + "norm1"] = ()
         if l.mixer == "latent_attention":
@@ -265,8 +362,34 @@ def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
             out[p + "mlp.router"] = (l.experts, W)
             out.update({p + "rg2": (W, W), p + "rg2.b": (W,)})
         out.update({p + "rg1": (W, W), p + "rg1.b": (W,)})
-    out["final.norm"] = (W,) if spec.layers and spec.layers[-1].form == "sandwich" else ()
+    out["final.norm"] = (W,) if spec.layers and spec.layers[-1].form in ("sandwich", "postnorm") else ()
     out["head"] = (spec.vocab, W)
+    return out
+
+
+def _postnorm_shapes(p: str, i: int, l: LayerSpec, W: int, taps: int) -> Dict[str, Tuple[int, ...]]:
+    out: Dict[str, Tuple[int, ...]] = {p + "norm1": (W,), p + "canon1": (W, taps), p + "dwa": (i + 2,)}
+    m = p + "mix."
+    if l.mixer == "delta":
+        qk, hv = l.kv_heads * l.dim, l.heads * l.vdim
+        out.update({m + "q": (qk, W), m + "q.conv": (qk, l.conv), m + "k": (qk, W), m + "k.conv": (qk, l.conv),
+                    m + "v": (hv, W), m + "v.conv": (hv, l.conv), m + "b": (l.heads, W), m + "A_log": (l.heads,),
+                    m + "norm": (l.vdim,), m + "a": (l.heads, W), m + "dt_bias": (l.heads,), m + "g": (hv, W), m + "o": (W, hv)})
+    else:
+        b = l.branches[0]
+        hv = b.heads * b.vdim
+        if b.kind == "window_attention":
+            out.update({m + "q": (b.heads * b.dim, W), m + "q.b": (b.heads * b.dim,), m + "k": (b.kv_heads * b.dim, W),
+                        m + "k.b": (b.kv_heads * b.dim,), m + "v": (b.kv_heads * b.vdim, W), m + "v.b": (b.kv_heads * b.vdim,),
+                        m + "rel": (b.rel_rows, b.heads), m + "vmix": (), m + "sink": (b.heads,), m + "o": (W, hv),
+                        m + "o.b": (W,)})
+        else:
+            out.update({m + "dq": (b.q_rank, W), m + "dq.norm": (b.q_rank,), m + "uq": (b.heads * (b.dim + b.rot_dims), b.q_rank),
+                        m + "dkv": (b.kv_rank + b.rot_dims, W), m + "dkv.norm": (b.kv_rank,), m + "uk": (b.heads * b.dim, b.kv_rank),
+                        m + "uv": (hv, b.kv_rank), m + "o": (W, hv)})
+    if l.ff_kind == "dense":
+        out.update({p + "norm2": (W,), p + "canon2": (W, taps), p + "mlp.gate": (l.ff, W), p + "mlp.up": (l.ff, W),
+                    p + "mlp.down": (W, l.ff)})
     return out
 
 
@@ -310,9 +433,21 @@ def init_weights(spec: LayeredSpec, seed: int = 0, device: str = "cpu") -> Dict[
     g.manual_seed(seed)
     w = {}
     sandwich = bool(spec.layers) and spec.layers[-1].form == "sandwich"
+    postnorm = bool(spec.layers) and spec.layers[-1].form == "postnorm"
     for name, shape in tensor_shapes(spec).items():
         leaf = name.split(".")[-1]
-        if sandwich and (leaf in ("norm1", "norm1b", "norm2", "norm2b") or name == "final.norm"):
+        if postnorm and leaf in ("canon1", "canon2"):
+            t = 0.3 * torch.randn(shape, generator=g)
+        elif postnorm and leaf == "dwa":
+            t = 0.15 * torch.randn(shape, generator=g)
+            t[-1] += 1.0                                         # mostly the layer's own result
+        elif postnorm and leaf in ("rel", "sink"):
+            t = torch.randn(shape, generator=g)
+        elif postnorm and leaf == "vmix":
+            t = 0.2 + 0.5 * torch.rand(shape, generator=g)
+        elif postnorm and leaf == "b" and name.split(".")[-2] in ("q", "k", "v", "o"):
+            t = 0.3 * torch.randn(shape, generator=g)
+        elif sandwich and (leaf in ("norm1", "norm1b", "norm2", "norm2b") or name == "final.norm"):
             t = 0.2 * torch.randn(shape, generator=g)          # stored as gain - 1
         elif sandwich and leaf == "b":
             t = 0.5 * torch.randn(shape, generator=g)
@@ -389,6 +524,10 @@ class BranchDesc(C.Structure):
         ("gate_cap", C.c_float), ("gate_bias", C.c_void_p),
         ("conv", C.c_int), ("norm_groups", C.c_int),
         ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("dt_bias", C.c_void_p), ("a_log", C.c_void_p), ("skip", C.c_void_p),
+        ("qk_norm", C.c_int), ("keep_first", C.c_int), ("rel_n", C.c_int), ("v_role", C.c_int),
+        ("sink", C.c_void_p), ("rel", C.c_void_p), ("v_bias", C.c_void_p), ("o_bias", C.c_void_p), ("v_mix", C.c_void_p),
+        ("kv_rank", C.c_int), ("q_rank", C.c_int),
+        ("w_uq", C.c_void_p), ("w_uk_t", C.c_void_p), ("w_uv", C.c_void_p), ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p),
     ]
 
 
@@ -411,6 +550,7 @@ class LayerDesc(C.Structure):
         ("norm_pre1", C.c_void_p), ("norm_post1", C.c_void_p), ("norm_pre2", C.c_void_p), ("norm_post2", C.c_void_p),
         ("ff_act", C.c_int), ("route_kind", C.c_int), ("route_norm", C.c_int), ("route_scale", C.c_float),
         ("w_router", C.c_void_p), ("router_rows", C.c_int), ("shared_ff", C.c_int), ("w_shared_up", C.c_void_p), ("w_shared_down", C.c_void_p),
+        ("canon_taps", C.c_int), ("canon1", C.c_void_p), ("canon2", C.c_void_p), ("depth_w", C.c_void_p), ("gate_act", C.c_int),
     ]
 
 
@@ -420,7 +560,7 @@ class LayeredModel(C.Structure):
         ("width", C.c_int), ("vocab", C.c_int), ("n_layers", C.c_int),
         ("eps", C.c_float), ("logit_softcap", C.c_float), ("final_norm_gain", C.c_float),
         ("embed", C.c_void_p), ("head", C.c_void_p), ("layers", C.POINTER(LayerDesc)), ("exact_f32", C.c_int),
-        ("final_norm_w", C.c_void_p),
+        ("final_norm_w", C.c_void_p), ("embed_scale", C.c_float),
     ]
 
 
@@ -536,6 +676,89 @@ def _pack_sandwich_layer(l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W:
             d.w_shared_down = dev(w[p + "mlp.shared.down"]).data_ptr()
 
 
+def _pack_postnorm_layer(spec: LayeredSpec, i: int, l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W: int, device, dev,
+                         keep: list, first_mix: int) -> None:
+    """Descriptor of a post-norm layer: gains as stored, input convolutions, depth weights, the mixer's projections stacked
+    into w_in; the distance-bias table expanded to one row per distance."""
+    f32 = torch.float32
+    m = p + "mix."
+    d.form = LAYER_POSTNORM
+    for f_ in ("o_q", "o_k", "o_v", "o_dkv", "o_gate", "o_beta", "o_a1", "o_g1", "o_rg1", "o_rg2", "o_router"):
+        setattr(d, f_, -1)
+    d.norm_gain = 1.0
+    d.norm_post1 = dev(w[p + "norm1"], f32).data_ptr()
+    d.canon_taps = spec.canon_taps
+    if spec.canon_taps >= 1:
+        d.canon1 = dev(w[p + "canon1"], f32).data_ptr()
+    d.depth_w = dev(w[p + "dwa"], f32).data_ptr()
+    if l.mixer == "delta":
+        d.mixer, d.heads, d.kv_heads, d.dim, d.vdim, d.conv = MIXER_CHANNEL_DELTA, l.heads, l.kv_heads, l.dim, l.vdim, l.conv
+        d.rank_a = d.rank_g = 0
+        d.gate_act = 1
+        qkv = torch.cat([w[m + "q"], w[m + "k"], w[m + "v"]], 0)      # adjacent: one run of convolution channels
+        parts = [("q", qkv), ("beta", w[m + "b"]), ("a1", w[m + "a"]), ("g1", w[m + "g"])]
+    else:
+        b = l.branches[0]
+        d.mixer, d.n_branches = MIXER_BRANCHES, 1
+        parts = [("q", w[m + "q"]), ("k", w[m + "k"]), ("v", w[m + "v"])] if b.kind == "window_attention" else \
+                [("q", w[m + "dq"]), ("k", w[m + "dkv"])]
+    w_in, offs = _stack_inputs([(n, t.to(device)) for n, t in parts], W, device)
+    keep.append(w_in)
+    d.w_in, d.n_in = w_in.data_ptr(), w_in.shape[0]
+    if l.mixer == "delta":
+        for n, o in offs.items():
+            setattr(d, "o_" + n, o)
+        d.o_k = d.o_q + l.kv_heads * l.dim
+        d.o_v = d.o_k + l.kv_heads * l.dim
+        d.w_o = dev(w[m + "o"]).data_ptr()
+        d.conv_w = dev(torch.cat([w[m + "q.conv"], w[m + "k.conv"], w[m + "v.conv"]], 0), f32).data_ptr()
+        d.dt_bias = dev(w[m + "dt_bias"], f32).data_ptr()
+        d.a_log = dev(w[m + "A_log"], f32).data_ptr()
+        d.out_norm = dev(w[m + "norm"], f32).data_ptr()
+    else:
+        b, c = l.branches[0], d.branch[0]
+        c.kind, c.heads, c.kv_heads, c.dim, c.vdim = BRANCHES[b.kind], b.heads, b.kv_heads or b.heads, b.dim, b.vdim
+        c.out_scale = 1.0
+        for f_ in ("o_q", "o_k", "o_v", "o_g", "o_z", "o_dt", "o_i", "o_f"):
+            setattr(c, f_, -1)
+        c.o_q, c.o_k = offs["q"], offs["k"]
+        c.w_o = dev(w[m + "o"]).data_ptr()
+        c.scale, c.window, c.rot_dims = b.scale, b.window, b.rot_dims
+        if b.rot_dims:
+            i2 = torch.arange(b.rot_dims // 2, dtype=torch.float64)
+            c.rot_freq = dev(torch.tensor(b.rot_base, dtype=torch.float64) ** (-2.0 * i2 / b.rot_dims), f32).data_ptr()
+        if b.kind == "window_attention":
+            c.o_v = offs["v"]
+            c.qk_norm, c.keep_first = int(b.qk_norm), b.keep_first
+            if b.biases:
+                c.q_bias, c.k_bias = dev(w[m + "q.b"], f32).data_ptr(), dev(w[m + "k.b"], f32).data_ptr()
+                c.v_bias, c.o_bias = dev(w[m + "v.b"], f32).data_ptr(), dev(w[m + "o.b"], f32).data_ptr()
+            if b.sink:
+                c.sink = dev(w[m + "sink"], f32).data_ptr()
+            if b.rel_rows:
+                rows = distance_rows(b.rel_rows, b.rel_far)
+                table = w[m + "rel"].float().cpu()[torch.tensor(rows)]          # [distance][head]
+                c.rel, c.rel_n = dev(table, f32).data_ptr(), len(rows)
+            if b.v_mix:
+                c.v_role = 1 if i == first_mix else 2
+                c.v_mix = dev(w[m + "vmix"].reshape(1), f32).data_ptr()
+        else:
+            c.kv_rank, c.q_rank = b.kv_rank, b.q_rank
+            c.w_uq = dev(w[m + "uq"]).data_ptr()
+            c.w_uk_t = dev(w[m + "uk"].reshape(b.heads, b.dim, b.kv_rank).transpose(1, 2)).data_ptr()      # [heads][kv_rank][dim]
+            c.w_uv = dev(w[m + "uv"]).data_ptr()
+            c.q_norm = dev(w[m + "dq.norm"], f32).data_ptr()
+            c.kv_norm = dev(w[m + "dkv.norm"], f32).data_ptr()
+    d.ff_kind = FF_NONE
+    if l.ff_kind == "dense":
+        d.ff_kind, d.ff_act, d.ff = FF_DENSE, ACT_SWIGLU, l.ff
+        d.norm_post2 = dev(w[p + "norm2"], f32).data_ptr()
+        if spec.canon_taps >= 1:
+            d.canon2 = dev(w[p + "canon2"], f32).data_ptr()
+        d.w_gu = dev(_interleave(w[p + "mlp.gate"].to(device), w[p + "mlp.up"].to(device))).data_ptr()
+        d.w_down = dev(w[p + "mlp.down"]).data_ptr()
+
+
 def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool = False) -> Tuple[LayeredModel, list]:
     """Device arrays in the engine's layout + the descriptor structs.  Returns (model, keepalive): the engine borrows
     the pointers, so `keepalive` has to live as long as the engine."""
@@ -554,6 +777,10 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
         m = p + "mix."
         if l.form == "sandwich":
             _pack_sandwich_layer(l, w, p, d, W, device, dev, keep)
+            continue
+        if l.form == "postnorm":
+            first_mix = next((j for j, x in enumerate(spec.layers) if x.branches and x.branches[0].v_mix), -1)
+            _pack_postnorm_layer(spec, i, l, w, p, d, W, device, dev, keep, first_mix)
             continue
         d.mixer, d.heads, d.dim, d.vdim = MIXERS[l.mixer], l.heads, l.dim, l.vdim
         d.norm_gain = float(w[p + "norm1"].float().item())
@@ -608,11 +835,13 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
     model = LayeredModel()
     model.width, model.vocab, model.n_layers = W, spec.vocab, len(spec.layers)
     model.eps, model.logit_softcap = spec.eps, spec.logit_softcap
+    postnorm = bool(spec.layers) and spec.layers[0].form == "postnorm"
     if w["final.norm"].dim() == 0:
         model.final_norm_gain = float(w["final.norm"].float().item())
     else:
-        model.final_norm_gain = 1.0
-        model.final_norm_w = dev(1.0 + w["final.norm"].float(), torch.float32).data_ptr()
+        model.final_norm_gain = 1.0          # sandwich models store gain - 1, post-norm models the gain itself
+        model.final_norm_w = dev(w["final.norm"].float() + (0.0 if postnorm else 1.0), torch.float32).data_ptr()
+    model.embed_scale = spec.embed_scale if postnorm else 1.0
     model.embed = dev(w["embed"]).data_ptr()
     model.head = dev(w["head"]).data_ptr()
     model.layers = C.cast(descs, C.POINTER(LayerDesc))

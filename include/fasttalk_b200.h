@@ -193,7 +193,13 @@ enum { FT_FF_NONE = 0, FT_FF_MOE = 1, FT_FF_DENSE = 2 };
  *   FT_LAYER_GATED:    the form above (one scalar-gain norm feeds both sublayers, sigmoid gates on the way back).
  *   FT_LAYER_SANDWICH: x += post1(mixer(pre1(x))); x += post2(ff(pre2(x))), each of the four an RMS norm with a gain per
  *                      coordinate, given as the gain itself (a checkpoint that stores gain - 1 is converted at load time). */
-enum { FT_LAYER_GATED = 0, FT_LAYER_SANDWICH = 1 };
+/*   FT_LAYER_POSTNORM: the sublayers read the stream itself, through a short causal convolution over time per coordinate
+ *                      (h = x + conv(x), taps canon_taps, the last column of the [width][taps] table weighs the current
+ *                      token; the last taps - 1 stream rows of each sublayer live in the session's state slot), and only
+ *                      their results are normed: x += post1(mixer(h1)); x += post2(ff(h2)).  With depth_w the stream that
+ *                      goes on is a weighted sum over depth, sum_j depth_w[j] X_j, X_0 the embedding output and X_(i+1)
+ *                      layer i's result before this averaging.  Takes any mixer of the family. */
+enum { FT_LAYER_GATED = 0, FT_LAYER_SANDWICH = 1, FT_LAYER_POSTNORM = 2 };
 enum { FT_ACT_SWIGLU = 0, FT_ACT_RELU2 = 1 };          /* expert: W_down (silu(W_gate h) * W_up h)  |  W_down relu(W_up h)^2 */
 enum { FT_ROUTE_SOFTMAX = 0, FT_ROUTE_SIGMOID = 1 };   /* router scores over all experts */
 
@@ -213,8 +219,21 @@ enum { FT_ROUTE_SOFTMAX = 0, FT_ROUTE_SIGMOID = 1 };   /* router scores over all
  *                               divided by its own root mean square, then gain out_norm and the gate sigmoid(g).
  *   FT_BRANCH_STATE_SPACE       x | B | C pass a short causal convolution (with bias) and SiLU; dt = softplus(dt + dt_bias);
  *                               a = exp(-exp(a_log) dt), b = dt, k = B, q = C (kv_heads groups of heads share them), v = x;
- *                               o += skip[head] * x; o *= silu(z); RMS norm in norm_groups equal parts, gain out_norm. */
-enum { FT_BRANCH_WINDOW_ATTENTION = 1, FT_BRANCH_DECAY_ATTENTION = 2, FT_BRANCH_MATRIX_MEMORY = 3, FT_BRANCH_STATE_SPACE = 4 };
+ *                               o += skip[head] * x; o *= silu(z); RMS norm in norm_groups equal parts, gain out_norm.
+ *   FT_BRANCH_LATENT_WINDOW     window attention over ONE shared key head whose cached key is [rotated part | normed latent]
+ *                               and whose value is the latent: queries pass a normed latent of their own (o_q: q_rank columns,
+ *                               gain q_norm, then w_uq into heads x (dim plain | rot_dims rotated)); o_k: kv_rank latent columns
+ *                               (gain kv_norm) followed by rot_dims columns of the shared rotated key part; per head the plain
+ *                               key is W_uk c and the value W_uv c, neither is formed: the plain query is folded through
+ *                               w_uk_t and the attended latent expanded through w_uv.  dim = plain size per head.
+ * Options of window attention (all off when zero / null): qk_norm (queries and keys divided by their root mean square per
+ * head, eps of the model, before rotation), keep_first (the first keep_first positions stay visible beyond the window, at
+ * their true distances), sink (fp32 [heads]: exp(sink_h) joins the softmax denominator, no key, no value), rel (fp32
+ * [rel_n][heads]: a bias by distance i - j, distances from rel_n - 1 on share the last row; added after scale and cap),
+ * v_bias, o_bias (fp32 [width], added to the branch's projected output), v_role (1: this layer's values are kept for the
+ * step as the "first" values; 2: v <- (1 - v_mix) v + v_mix v_first before they are cached). */
+enum { FT_BRANCH_WINDOW_ATTENTION = 1, FT_BRANCH_DECAY_ATTENTION = 2, FT_BRANCH_MATRIX_MEMORY = 3, FT_BRANCH_STATE_SPACE = 4,
+       FT_BRANCH_LATENT_WINDOW = 5 };
 typedef struct {
     int kind;                  /* FT_BRANCH_* */
     int heads, kv_heads;       /* head h reads key (value) head h / (heads / kv_heads); state space: kv_heads = groups */
@@ -241,6 +260,20 @@ typedef struct {
     const float* dt_bias;      /* fp32 [heads] */
     const float* a_log;        /* fp32 [heads] */
     const float* skip;         /* fp32 [heads] */
+    /* window attention options */
+    int qk_norm, keep_first, rel_n, v_role;
+    const float* sink;         /* fp32 [heads] */
+    const float* rel;          /* fp32 [rel_n][heads] */
+    const float* v_bias;       /* fp32 [kv_heads * vdim] */
+    const float* o_bias;       /* fp32 [width] */
+    const float* v_mix;        /* fp32 [1] */
+    /* latent window attention */
+    int kv_rank, q_rank;
+    const void* w_uq;          /* bf16 [heads * (dim + rot_dims)][q_rank] */
+    const void* w_uk_t;        /* bf16 [heads][kv_rank][dim] */
+    const void* w_uv;          /* bf16 [heads * vdim][kv_rank] */
+    const float* q_norm;       /* fp32 [q_rank] */
+    const float* kv_norm;      /* fp32 [kv_rank] */
 } ft_branch_desc;
 
 typedef struct {
@@ -293,6 +326,14 @@ typedef struct {
     int shared_ff;             /* 0 = no shared expert */
     const void* w_shared_up;   /* bf16 [shared_ff (x 2, paired, for FT_ACT_SWIGLU)][width] */
     const void* w_shared_down; /* bf16 [width][shared_ff] */
+    /* ---- FT_LAYER_POSTNORM ---- */
+    int canon_taps;            /* taps of the input convolutions (1 = the sublayers read (1 + w) x; 0 = they read x) */
+    const float* canon1;       /* fp32 [width][canon_taps], mixer input */
+    const float* canon2;       /* fp32 [width][canon_taps], feed-forward input */
+    const float* depth_w;      /* fp32 [layer index + 2] or null */
+    /* channel delta with rank_a == 0: the decay pre-activation is one column per head of w_in at o_a1 and dt_bias is [heads]
+     * (one decay per head and token); with rank_g == 0 the gate is heads * vdim columns of w_in at o_g1 */
+    int gate_act;              /* channel delta: 0 = sigmoid(gate), 1 = silu(gate) */
 } ft_layer_desc;
 
 typedef struct {
@@ -308,6 +349,7 @@ typedef struct {
                                   the tensor cores (tcgen05) from bf16 hi + lo planes of the fp32 activations with fp32
                                   accumulation; norms, scores, softmax, router, recurrence and residual stay fp32 */
     const float* final_norm_w; /* fp32 [width] or null: a gain per coordinate instead of final_norm_gain */
+    float embed_scale;         /* FT_LAYER_POSTNORM models: the embedding output is embed[token] * embed_scale (0 = 1) */
 } ft_layered_model;
 
 /* cfg: vocab, max_batch, max_batched_tokens, num_pages, max_context, max_sessions (= state slots), eos, debug_logit_rows
