@@ -186,3 +186,13 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         if trail is not None:
             trail.append(x)
     return (rms_unit(x, eps) * w["final.norm"]) @ w["head"].T
+
+
+def greedy(cfg: Dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """n_new tokens of argmax decoding after `prompt` (the whole sequence is recomputed for every token)."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(cfg, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
