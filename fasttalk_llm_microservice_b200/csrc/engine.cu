@@ -1520,7 +1520,7 @@ static int engine_init_layered(Engine* e) {
             FT_REQUIRE(d.norm_pre1 && d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.norm_pre2 && d.norm_post2)),
                        "engine: sandwich layer %d lacks norm gains", l);
         } else {
-            FT_REQUIRE(d.form == FT_LAYER_GATED && d.rg_bias && d.o_rg1 >= 0 && d.mixer != FT_MIXER_BRANCHES && d.rank_a >= 1 && d.rank_g >= 1,
+            FT_REQUIRE(d.form == FT_LAYER_GATED && d.rg_bias && d.o_rg1 >= 0 && d.mixer != FT_MIXER_BRANCHES,
                        "engine: gated layer %d is incomplete (it takes latent attention or channel delta)", l);
         }
         n_in_max = std::max(n_in_max, d.n_in);
