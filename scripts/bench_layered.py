@@ -2,6 +2,7 @@
 
     python bench.py --design gitozen  [--sizes s,m] [--arms gitozen,llama] [--steps K] [--warmup W]
     python bench.py --design gedelorn [--sizes s,m] [--arms gedelorn,gitozen,llama] [--steps K] [--warmup W]
+    python bench.py --design vonedra  [--sizes s,m] [--arms vonedra,gedelorn,gitozen,llama] [--steps K] [--warmup W]
 
 For every size all arms get the same width, depth, heads x head size, active feed-forward width (top x expert ff =
 Llama's ffn) and vocabulary.  Gedelorn's closest relative in the framework is Gitozen (the same engine path: stacked
@@ -68,6 +69,26 @@ def gedelorn_spec(name, c):
     return spec_from_config(cfg, name=f"gedelorn-{name}")
 
 
+def vonedra_spec(name, c):
+    """Four post-norm layers with a dense feed-forward each: attention (window 512 that keeps the first 4 tokens, a quarter as
+    many key heads, 32 distance rows), delta rule, attention, latent window attention (64 rotated coordinates, window 512).
+    Heads x head size as in the other arms; input convolutions of 4 taps."""
+    from fasttalk_llm_microservice_b200.layered import spec_from_config
+    W, H, D = c["width"], c["heads"], c["dim"]
+    att = {"type": "attention", "mixer": {"bias_max": 512, "dim": D, "heads": H, "kv_heads": max(1, H // 4),
+                                          "mask": {"keep_first": 4, "size": 512}, "scale": D ** -0.5, "v_mix": True, "vdim": D}}
+    dlt = {"type": "delta", "mixer": {"conv": 4, "dim": D, "heads": H, "kv_heads": H, "vdim": D}}
+    lat = {"type": "latent_attention", "mixer": {"dim": D, "heads": H, "kv_rank": c["kv_rank"], "mask": {"size": 512},
+                                                 "q_rank": 2 * c["kv_rank"], "rot": {"base": 1e4, "dims": 64}, "rot_dim": 64,
+                                                 "scale": (D + 64) ** -0.5, "vdim": D}}
+    dense = {"ff": c["top"] * c["ff"], "kind": "dense"}
+    layers = [{**att, "mlp": dense}, {**dlt, "mlp": dense}, {**att, "mlp": dense}, {**lat, "mlp": dense}]
+    cfg = {"architecture": "Vonedra", "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-6},
+           "vocab": c["vocab"], "width": W}
+    shapes = {"l0.mix.rel": (32, H), "l2.mix.rel": (32, H), "l3.mix.dq": (2 * c["kv_rank"], W)}
+    return spec_from_config(cfg, shapes, name=f"vonedra-{name}")
+
+
 def llama_spec(name, c):
     from fasttalk_llm_microservice_b200.model_spec import ModelSpec
     return ModelSpec(name=f"llama-{name}", hidden=c["width"], ffn=c["top"] * c["ff"], layers=len(c["order"]),
@@ -130,9 +151,10 @@ def run(args) -> None:
         c = SIZES[name]
         row = {"config": c}
         design = getattr(args, "design", "") or "gitozen"
-        for arm in (getattr(args, "arms", "") or ("gedelorn,gitozen,llama" if design == "gedelorn" else "gitozen,llama")).split(","):
-            if arm in ("gitozen", "gedelorn"):
-                spec = gitozen_spec(name, c) if arm == "gitozen" else gedelorn_spec(name, c)
+        default_arms = {"vonedra": "vonedra,gedelorn,gitozen,llama", "gedelorn": "gedelorn,gitozen,llama"}.get(design, "gitozen,llama")
+        for arm in (getattr(args, "arms", "") or default_arms).split(","):
+            if arm in ("gitozen", "gedelorn", "vonedra"):
+                spec = {"gitozen": gitozen_spec, "gedelorn": gedelorn_spec, "vonedra": vonedra_spec}[arm](name, c)
                 w = init_layered(spec, seed=0, device="cuda")
             else:
                 spec = llama_spec(name, c)
