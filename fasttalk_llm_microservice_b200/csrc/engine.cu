@@ -205,7 +205,9 @@ struct Layered {
     bool tensor = false;               // projections that tile run on the tensor cores (ft_layered_model.exact_f32 == 0)
     // post-norm layers: the stream as every layer left it [n_layers + 1][t_max][width] (the sum over depth reads them all), the
     // values of the first value-mixing attention layer of the step, the staging rows of latent window attention
-    float *hist = nullptr, *v_first = nullptr, *lstage = nullptr;
+    // resid2: the stream between a layer's two sublayers (the joint kernel that forms the feed-forward's input reads
+    // neighbouring rows of the old stream while it writes the new one)
+    float *hist = nullptr, *v_first = nullptr, *lstage = nullptr, *resid2 = nullptr;
     bool postnorm = false;
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
@@ -566,6 +568,7 @@ static int forward(Engine* e, const Batch& b) {
 // as bf16 hi + lo planes (`hi` / `lo` if the producer already wrote them, else staged here), fp32 out.  Otherwise, and always
 // in the exact-fp32 form, the CUDA-core kernels.
 constexpr int kTensorMinRows = 9;
+constexpr int kFuseCanonRows = 256;          // steps up to this many rows form the feed-forward's input inside the post-norm kernel
 constexpr int kMoeTensorMinPairs = 256;      // (token, choice) pairs from which the experts run as per-expert tensor-core GEMMs
 static int dense(Engine* e, const float* A, const void* hi, const void* lo, const void* W, float* C, int T, int N, int K,
                  float softcap = 0.f) {
@@ -816,16 +819,16 @@ static int forward_layered(Engine* e, const Batch& b) {
         FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain,
                                  L.layers[0].d.form == FT_LAYER_SANDWICH ? L.layers[0].d.norm_pre1 : nullptr, st));
     launched();
-    // what a sublayer of a post-norm layer reads: the stream plus its short convolution over time
-    auto canon = [&](const LayeredLayer& ll, int which) -> int {
+    // what the mixer of a post-norm layer reads: the stream plus its short convolution over time
+    auto canon = [&](const LayeredLayer& ll) -> int {
         const ft_layer_desc& c = ll.d;
         CanonArgs ca;
         ca.x = e->resid; ca.hn = L.hn; ca.hi = hn_hi; ca.lo = hn_lo; ca.W = W;
-        ca.w = c.canon_taps >= 1 ? (which ? c.canon2 : c.canon1) : nullptr; ca.taps = c.canon_taps;
-        ca.state = L.state; ca.slot_stride = (long long)L.slot_stride; ca.tail_off = (long long)ll.canon_off[which];
+        ca.w = c.canon_taps >= 1 ? c.canon1 : nullptr; ca.taps = c.canon_taps;
+        ca.state = L.state; ca.slot_stride = (long long)L.slot_stride; ca.tail_off = (long long)ll.canon_off[0];
         ca.seq_rows = d + m.o_rows; ca.req_start = d + m.o_xstart; ca.req_pos0 = d + m.o_xpos0; ca.req_slot = d + m.o_xslot;
-        FT_TRY(launch_canon(ca, T, b.n_req, st));
-        launched(c.canon_taps > 1 ? 2 : 1);
+        FT_TRY(launch_canon(ca, T, st));
+        launched();
         return 0;
     };
     for (int l = 0; l < M.n_layers; ++l) {
@@ -833,7 +836,7 @@ static int forward_layered(Engine* e, const Batch& b) {
         const ft_layer_desc& c = ll.d;
         const bool sandwich = c.form == FT_LAYER_SANDWICH;
         const int ld = c.n_in;              // row stride of this layer's projection outputs
-        if (c.form == FT_LAYER_POSTNORM) FT_TRY(canon(ll, 0));
+        if (c.form == FT_LAYER_POSTNORM) FT_TRY(canon(ll));
         FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_in, L.proj, T, c.n_in, W));
         const float *y0 = L.mix, *y1 = nullptr;      // the mixer's result: s0 * y0 + s1 * y1, each [T][width]
         float s0 = 1.f, s1 = 1.f;
@@ -909,19 +912,47 @@ static int forward_layered(Engine* e, const Batch& b) {
         if (c.form == FT_LAYER_POSTNORM) {
             // x += norm(mixer);  x += norm(ff(x + conv(x)));  the layer's result joins the depth history and the stream that
             // goes on is the weighted sum over it
+            // One kernel per joint: it also keeps the rows the sublayer read for the next step's convolution and forms what
+            // reads the stream next (the feed-forward's input, or the sum over depth).
             const bool has_ff = c.ff_kind != FT_FF_NONE;
+            // In the fused form a row's CTA forms its taps - 1 predecessors again; that pays while launches, not bytes, bound
+            // the step.  Both forms add the same numbers in the same order.
+            const bool fuse_next = c.canon_taps >= 1 && T <= kFuseCanonRows;
+            auto joint = [&](PostNormArgs& p, int which) {
+                p.W = W; p.eps = M.eps; p.taps = c.canon_taps;
+                p.state = L.state; p.slot_stride = (long long)L.slot_stride;
+                p.save_off = c.canon_taps > 1 ? (long long)ll.canon_off[which] : -1;
+                p.seq_rows = d + m.o_rows; p.req_start = d + m.o_xstart; p.req_pos0 = d + m.o_xpos0; p.req_slot = d + m.o_xslot;
+            };
+            auto ends_layer = [&](PostNormArgs& p) { p.x_out = e->resid; p.hist = L.hist; p.depth_w = c.depth_w; p.k = l + 1; p.t_stride = e->t_max; };
             PostNormArgs pa;
-            pa.x = e->resid; pa.W = W; pa.eps = M.eps; pa.y0 = y0; pa.y1 = y1; pa.s0 = s0; pa.s1 = s1; pa.post_w = c.norm_post1;
+            joint(pa, 0);
+            pa.x = e->resid; pa.y0 = y0; pa.y1 = y1; pa.s0 = s0; pa.s1 = s1; pa.post_w = c.norm_post1;
             if (c.mixer == FT_MIXER_BRANCHES) { pa.b0 = c.branch[0].o_bias; pa.b1 = y1 ? c.branch[1].o_bias : nullptr; }
-            auto ends_layer = [&](PostNormArgs& p) { p.hist = L.hist; p.depth_w = c.depth_w; p.k = l + 1; p.t_stride = e->t_max; };
-            if (!has_ff) ends_layer(pa);
+            if (!has_ff) {
+                ends_layer(pa);
+            } else if (fuse_next) {              // the feed-forward's input in the same pass
+                pa.x_out = L.resid2; pa.cw = c.canon2; pa.read_off = (long long)ll.canon_off[1];
+                pa.hn = L.hn; pa.hi = hn_hi; pa.lo = hn_lo;
+            } else {
+                pa.x_out = L.resid2;
+            }
             FT_TRY(launch_postnorm(pa, T, st));
             launched();
             if (has_ff) {
-                FT_TRY(canon(ll, 1));
+                if (!fuse_next) {                 // the feed-forward's input in a pass of its own
+                    CanonArgs ca;
+                    ca.x = L.resid2; ca.hn = L.hn; ca.hi = hn_hi; ca.lo = hn_lo; ca.W = W;
+                    ca.w = c.canon_taps >= 1 ? c.canon2 : nullptr; ca.taps = c.canon_taps;
+                    ca.state = L.state; ca.slot_stride = (long long)L.slot_stride; ca.tail_off = (long long)ll.canon_off[1];
+                    ca.seq_rows = d + m.o_rows; ca.req_start = d + m.o_xstart; ca.req_pos0 = d + m.o_xpos0; ca.req_slot = d + m.o_xslot;
+                    FT_TRY(launch_canon(ca, T, st));
+                    launched();
+                }
                 FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_gu, c.w_down, c.ff, c.ff_act, L.mix, T));
                 PostNormArgs pf;
-                pf.x = e->resid; pf.W = W; pf.eps = M.eps; pf.y0 = L.mix; pf.post_w = c.norm_post2;
+                joint(pf, 1);
+                pf.x = L.resid2; pf.y0 = L.mix; pf.post_w = c.norm_post2;
                 ends_layer(pf);
                 FT_TRY(launch_postnorm(pf, T, st));
                 launched();
@@ -1669,6 +1700,7 @@ static int engine_init_layered(Engine* e) {
     if (use_hist) FT_TRY(alloc(&L.hist, (size_t)(M.n_layers + 1) * T * W * 4));
     if (vfirst_cols) FT_TRY(alloc(&L.v_first, T * vfirst_cols * 4));
     if (lstage_cols) FT_TRY(alloc(&L.lstage, T * lstage_cols * 4));
+    if (L.postnorm) FT_TRY(alloc(&L.resid2, T * W * 4));
     FT_TRY(alloc(&L.ffa, T * act_cols * 2 * 4));
     FT_TRY(alloc(&L.ffb, T * act_cols * 4));
     FT_TRY(alloc(&L.rlog, T * e_max_s * 4));
@@ -1740,7 +1772,7 @@ static void engine_free(Engine* e) {
         cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.kv_cache); cudaFree(L.bq); cudaFree(L.bv); cudaFree(L.bo); cudaFree(L.bfin); cudaFree(L.ab); cudaFree(L.gates);
-        cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage);
+        cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage); cudaFree(L.resid2);
         cudaFree(L.floor); cudaFree(L.mix2); cudaFree(L.ffa); cudaFree(L.ffb); cudaFree(L.rlog);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);

@@ -290,23 +290,27 @@ int launch_readout(const ReadoutArgs& a, int T, cudaStream_t stream);
 // x[t] = embed[token] * scale; the same row into hist (X_0) when given
 int launch_embed_scale(const int* tokens, const void* embed, float scale, float* x, float* hist, int T, int W, cudaStream_t stream);
 // What a sublayer reads: hn[t] = x[t] + sum_j w[:, j] x[t - taps + 1 + j] over the rows of t's own sequence; rows before the
-// step come from the slot's tail [taps - 1][W] at tail_off (zeros before position 0).  hi / lo (may be null): hn as planes.
-// w null: hn = x.  Afterwards the tail takes the sequence's last taps - 1 rows.
+// step come from the slot's ring [taps - 1][W] at tail_off, where the row of position p sits at p % (taps - 1) (zeros before
+// position 0).  hi / lo (may be null): hn as planes.  w null: hn = x.  The ring is written by launch_postnorm.
 struct CanonArgs {
     const float* x = nullptr;
     float* hn = nullptr;
     void *hi = nullptr, *lo = nullptr;
     const float* w = nullptr;                     // [W][taps]
     int taps = 0, W = 0;
-    float* state = nullptr;
+    const float* state = nullptr;
     long long slot_stride = 0, tail_off = 0;
     const int *seq_rows = nullptr, *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
 };
-int launch_canon(const CanonArgs& a, int T, int n_req, cudaStream_t stream);
-// x += rms(y0 + b0 [+ y1 + b1]) * post_w.  With hist: the new row is X_k (written to hist[k]) and the stream becomes
-// sum_{j <= k} depth_w[j] hist[j]; hist is [n][t_stride][W].
+int launch_canon(const CanonArgs& a, int T, cudaStream_t stream);
+// x_out = x + rms(y0 + b0 [+ y1 + b1]) * post_w (x_out may be x unless cw is given).
+//   save_off >= 0: the last taps - 1 rows of x of every sequence (what the sublayer read) go into the ring at save_off first.
+//   hist: the new row is X_k (written to hist[k]) and x_out becomes sum_{j <= k} depth_w[j] hist[j]; hist is [n][t_stride][W].
+//   cw:   the next sublayer's input hn (+ planes) = x_out + conv(x_out) with weights cw [W][taps], rows before the step from
+//         the ring at read_off.
 struct PostNormArgs {
-    float* x = nullptr;
+    const float* x = nullptr;
+    float* x_out = nullptr;
     const float *y0 = nullptr, *y1 = nullptr, *b0 = nullptr, *b1 = nullptr;
     float s0 = 1.f, s1 = 1.f;
     const float* post_w = nullptr;
@@ -316,6 +320,13 @@ struct PostNormArgs {
     long long t_stride = 0;
     int W = 0;
     float eps = 0.f;
+    int taps = 0;
+    float* state = nullptr;
+    long long slot_stride = 0, save_off = -1, read_off = 0;
+    const int *seq_rows = nullptr, *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+    const float* cw = nullptr;
+    float* hn = nullptr;
+    void *hi = nullptr, *lo = nullptr;
 };
 int launch_postnorm(const PostNormArgs& a, int T, cudaStream_t stream);
 // out[i] = rms(x[rows ? rows[i] : i]) * w (gain per coordinate) or * gain

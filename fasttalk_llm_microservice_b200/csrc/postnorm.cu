@@ -2,9 +2,10 @@
 //
 //   embedding            x = embed[token] * scale, also kept as X_0 of the depth history
 //   input convolution    what a sublayer reads: hn = x + conv(x), a causal convolution over time per coordinate whose
-//                        inputs before the step's first row come from the slot's tail of stream rows; then the new tail
-//   post norm            x += rms(y) * gain for a sublayer's result y (one or two branch results with their biases); at a
-//                        layer's end also the weighted sum over depth: the new row is X_k, the stream becomes sum_j w_j X_j
+//                        inputs before the step's first row come from the slot's ring of stream rows
+//   post norm            x += rms(y) * gain for a sublayer's result y (one or two branch results with their biases), fused
+//                        with what follows it: the ring's new rows, and either the next sublayer's input convolution or, at a
+//                        layer's end, the weighted sum over depth (the new row is X_k, the stream becomes sum_j w_j X_j)
 //   row norms            the model's last norm over the wanted rows; a run of columns normed to a place (latents)
 #include "common.cuh"
 #include "ft_internal.h"
@@ -51,13 +52,17 @@ int launch_embed_scale(const int* tokens, const void* embed, float scale, float*
 }
 
 // ------------------------------------------------------------------ input convolution
+// The rows a convolution needs from before the step live in the session's slot as a ring over positions: the stream row of
+// position p (as the sublayer saw it) sits in ring[p % (taps - 1)].  The ring is READ by the kernel that forms the
+// sublayer's input and WRITTEN by the post-norm kernel that follows the sublayer (it still holds the rows the sublayer read):
+// two launches in stream order, so a step never reads a ring entry that it has already replaced.
 constexpr int kCanonMaxTaps = 17;
 __global__ void __launch_bounds__(256) canon_kernel(CanonArgs a) {
-    const int t = blockIdx.x, W = a.W, taps = a.taps;
+    const int t = blockIdx.x, W = a.W, taps = a.taps, keep = taps - 1;
     const int req = a.seq_rows[t];
     const int r = t - a.req_start[req];              // index inside this step's portion
     const int pos0 = a.req_pos0[req];
-    const float* tail = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.tail_off;      // [taps - 1][W], oldest first
+    const float* ring = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.tail_off;      // [taps - 1][W]
     __nv_bfloat16 *hi = (__nv_bfloat16*)a.hi, *lo = (__nv_bfloat16*)a.lo;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float s = a.x[(size_t)t * W + c];
@@ -67,7 +72,7 @@ __global__ void __launch_bounds__(256) canon_kernel(CanonArgs a) {
                 const int back = taps - 1 - i;
                 float v;
                 if (r - back >= 0) v = a.x[(size_t)(t - back) * W + c];
-                else if (pos0 + r - back >= 0) v = tail[(size_t)(taps - 1 + r - back) * W + c];
+                else if (pos0 + r - back >= 0) v = ring[(size_t)((pos0 + r - back) % keep) * W + c];
                 else v = 0.f;
                 acc = fmaf(a.w[(size_t)c * taps + i], v, acc);
             }
@@ -77,64 +82,101 @@ __global__ void __launch_bounds__(256) canon_kernel(CanonArgs a) {
         if (hi) planes_put(hi, lo, (size_t)t * W + c, s);
     }
 }
-// New tail per (request, coordinate): the last taps - 1 entries of (old tail ++ this step's rows).
-__global__ void canon_tail_kernel(CanonArgs a, int n_req) {
-    const int req = blockIdx.y, W = a.W;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= W || req >= n_req) return;
-    const int row0 = a.req_start[req], n = a.req_start[req + 1] - row0, pos0 = a.req_pos0[req], keep = a.taps - 1;
-    float* tail = a.state + (size_t)a.req_slot[req] * a.slot_stride + a.tail_off + c;
-    float v[kCanonMaxTaps - 1];
-    for (int i = 0; i < keep; ++i) {
-        const int src = n + i;                       // index into old tail (keep entries) ++ rows (n entries)
-        if (src < keep) v[i] = pos0 > 0 ? tail[(size_t)src * W] : 0.f;
-        else v[i] = a.x[(size_t)(row0 + src - keep) * W + c];
-    }
-    for (int i = 0; i < keep; ++i) tail[(size_t)i * W] = v[i];
-}
-int launch_canon(const CanonArgs& a, int T, int n_req, cudaStream_t stream) {
+int launch_canon(const CanonArgs& a, int T, cudaStream_t stream) {
     FT_REQUIRE(a.x && a.hn && a.W >= 1, "input convolution: missing operands");
     FT_REQUIRE(!a.w || (a.taps >= 1 && a.taps <= kCanonMaxTaps && a.state), "input convolution: %d taps are beyond %d", a.taps,
                kCanonMaxTaps);
     canon_kernel<<<T, 256, 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
-    if (a.w && a.taps > 1) {
-        canon_tail_kernel<<<dim3((a.W + 127) / 128, n_req), 128, 0, stream>>>(a, n_req);
-        FT_CHECK_CUDA(cudaGetLastError());
-    }
     return 0;
 }
 
-// ------------------------------------------------------------------ post norm and the sum over depth
+// ------------------------------------------------------------------ post norm, the sum over depth, the next input
+// One kernel per sublayer joint, one CTA per row t:
+//   (1) the row the sublayer read goes into its ring when it is among the last taps - 1 of its sequence in this step;
+//   (2) v = x[t] + rms(y[t]) * post_w;
+//   (3) at a layer's end: hist[k][t] = v and the stream becomes sum_j depth_w[j] hist[j][t];
+//   (4) otherwise, with cw: the NEXT sublayer's input hn[t] = v + sum_i cw[:, i] v[t - taps + 1 + i].  The earlier rows of
+//       the step are formed again from their own x and y (a row's norm needs nothing but that row), rows before the step
+//       come from the next sublayer's ring.  The new rows go to x_out, a buffer of its own, since the CTAs of the following
+//       rows read the old x[t].
+__device__ __forceinline__ float post_y(const PostNormArgs& a, size_t i, int c) {
+    float y = a.y0[i] + (a.b0 ? a.b0[c] : 0.f);
+    if (a.y1) y = a.s0 * y + a.s1 * (a.y1[i] + (a.b1 ? a.b1[c] : 0.f));
+    else if (a.s0 != 1.f) y *= a.s0;
+    return y;
+}
 __global__ void __launch_bounds__(256) postnorm_kernel(PostNormArgs a) {
     __shared__ float red[33];
-    extern __shared__ float row[];
+    extern __shared__ float sm[];
     const int t = blockIdx.x, W = a.W;
-    float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float y = a.y0[(size_t)t * W + c] + (a.b0 ? a.b0[c] : 0.f);
-        if (a.y1) y = a.s0 * y + a.s1 * (a.y1[(size_t)t * W + c] + (a.b1 ? a.b1[c] : 0.f));
-        else if (a.s0 != 1.f) y *= a.s0;
-        row[c] = y;
-        ss += y * y;
+    float* row = sm;                                  // [W] y of the row at hand
+    float* acc = sm + W;                              // [W] the convolution's sum (only with cw)
+    int r = 0, pos0 = 0, n = 1;
+    float* slot = nullptr;
+    if (a.seq_rows) {
+        const int req = a.seq_rows[t];
+        r = t - a.req_start[req];
+        n = a.req_start[req + 1] - a.req_start[req];
+        pos0 = a.req_pos0[req];
+        slot = a.state + (size_t)a.req_slot[req] * a.slot_stride;
     }
-    ss = block_sum(ss, red);
-    const float r = 1.f / sqrtf(ss / (float)W + a.eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float v = a.x[(size_t)t * W + c] + row[c] * r * a.post_w[c];
-        if (a.hist) {
-            a.hist[((size_t)a.k * a.t_stride + t) * W + c] = v;
-            if (a.depth_w) {
-                v *= a.depth_w[a.k];
-                for (int j = a.k - 1; j >= 0; --j) v = fmaf(a.depth_w[j], a.hist[((size_t)j * a.t_stride + t) * W + c], v);
+    const int keep = a.taps - 1;
+    if (a.save_off >= 0 && keep > 0 && r >= n - keep) {
+        float* ring = slot + a.save_off + (size_t)((pos0 + r) % keep) * W;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) ring[c] = a.x[(size_t)t * W + c];
+    }
+    const int first = a.cw ? keep : 0;                // how many earlier rows are formed again
+    if (a.cw)
+        for (int c = threadIdx.x; c < W; c += blockDim.x) acc[c] = 0.f;
+    for (int b = first; b >= 0; --b) {
+        const int rb = r - b;                         // uniform over the CTA
+        const float* cwb = a.cw ? a.cw + (a.taps - 1 - b) : nullptr;
+        if (rb < 0) {
+            if (pos0 + rb < 0) continue;
+            const float* ring = slot + a.read_off + (size_t)((pos0 + rb) % keep) * W;
+            for (int c = threadIdx.x; c < W; c += blockDim.x) acc[c] = fmaf(cwb[(size_t)c * a.taps], ring[c], acc[c]);
+            continue;
+        }
+        const size_t base = (size_t)(t - b) * W;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float y = post_y(a, base + c, c);
+            row[c] = y;
+            ss += y * y;
+        }
+        ss = block_sum(ss, red);
+        const float rs = 1.f / sqrtf(ss / (float)W + a.eps);
+        if (b > 0) {
+            for (int c = threadIdx.x; c < W; c += blockDim.x)
+                acc[c] = fmaf(cwb[(size_t)c * a.taps], a.x[base + c] + row[c] * rs * a.post_w[c], acc[c]);
+            continue;
+        }
+        __nv_bfloat16 *hi = (__nv_bfloat16*)a.hi, *lo = (__nv_bfloat16*)a.lo;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            float v = a.x[base + c] + row[c] * rs * a.post_w[c];
+            if (a.hist) {
+                a.hist[((size_t)a.k * a.t_stride + t) * W + c] = v;
+                if (a.depth_w) {
+                    v *= a.depth_w[a.k];
+                    for (int j = a.k - 1; j >= 0; --j) v = fmaf(a.depth_w[j], a.hist[((size_t)j * a.t_stride + t) * W + c], v);
+                }
+            }
+            a.x_out[base + c] = v;
+            if (a.cw) {
+                const float h = v + fmaf(cwb[(size_t)c * a.taps], v, acc[c]);
+                a.hn[base + c] = h;
+                if (hi) planes_put(hi, lo, base + c, h);
             }
         }
-        a.x[(size_t)t * W + c] = v;
     }
 }
 int launch_postnorm(const PostNormArgs& a, int T, cudaStream_t stream) {
-    FT_REQUIRE(a.x && a.y0 && a.post_w && a.W >= 1, "post norm: missing operands");
-    postnorm_kernel<<<T, 256, (size_t)a.W * 4, stream>>>(a);
+    FT_REQUIRE(a.x && a.x_out && a.y0 && a.post_w && a.W >= 1, "post norm: missing operands");
+    FT_REQUIRE(!a.cw || (a.x_out != a.x && a.hn && !a.hist && a.taps >= 1 && a.taps <= kCanonMaxTaps && (a.taps == 1 || a.seq_rows)),
+               "post norm: the fused input convolution needs a second stream buffer and the step's rows");
+    FT_REQUIRE(a.save_off < 0 || a.taps <= 1 || a.seq_rows, "post norm: saving rows needs the step's rows");
+    postnorm_kernel<<<T, 256, (size_t)a.W * 8, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
