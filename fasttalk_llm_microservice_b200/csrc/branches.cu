@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
         const float* kr = a.cache + base + (size_t)g * a.dim;
         float s = 0.f;
         if (VEC) {
+#pragma unroll 8
             for (int c = 0; c < a.dim; c += 4) {
                 const float4 kv = *reinterpret_cast<const float4*>(kr + c);
                 const float4 qv = *reinterpret_cast<const float4*>(sq + c);
@@ -216,16 +217,30 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
 #pragma unroll
         for (int i = 0; i < VPL; ++i) acc[i] *= corr;
         m = m_new;
-        const int cnt = min(32, n - b0);
-        for (int x = 0; x < cnt; ++x) {
-            const float px = __shfl_sync(0xffffffffu, pj, x);
-            const long long bx = __shfl_sync(0xffffffffu, base, x);
-            const float* vr = a.cache + bx + (size_t)a.G * a.dim + (size_t)g * a.vdim;
+        // all 32 keys of the block, four at a time so that their value loads are in flight together; a lane beyond the block's
+        // end holds weight 0 and the (valid) row of position p
+        for (int x0 = 0; x0 < 32; x0 += 4) {
+            if (x0 >= n - b0) break;
+            float px[4];
+            const float* vr[4];
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) {
-                const int c = lane + 32 * i;
-                if (c < a.vdim) acc[i] = fmaf(px, vr[c], acc[i]);
+            for (int u = 0; u < 4; ++u) {
+                px[u] = __shfl_sync(0xffffffffu, pj, x0 + u);
+                const long long bx = __shfl_sync(0xffffffffu, base, x0 + u);
+                vr[u] = a.cache + bx + (size_t)a.G * a.dim + (size_t)g * a.vdim;
             }
+            float vv[4][VPL];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) {
+                    const int c = lane + 32 * i;
+                    vv[u][i] = c < a.vdim ? vr[u][c] : 0.f;
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) acc[i] = fmaf(px[u], vv[u][i], acc[i]);
         }
     }
     if (lane == 0) { sm[wid] = m; sl[wid] = l; }
