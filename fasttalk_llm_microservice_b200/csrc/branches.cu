@@ -166,6 +166,25 @@ __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
     }
 }
 
+// two fp32 numbers in one 64-bit register and the two-wide fp32 multiply-add of sm_100 (each half rounds as the scalar one)
+typedef unsigned long long f32x2;      // two fp32 numbers in one 64-bit register
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 constexpr int kWinWarps = 4;
 template <int VPL, bool VEC>
 __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs a) {
@@ -307,13 +326,13 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
     bool rv[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) { rv[i] = 2 * ry + i < rows_used; pr[i] = p_first + (2 * ry + i) / grp; }
-    float acc[8][VK][4];
+    f32x2 acc[8][VK][2];                              // value columns (4 ox, + 1) and (+ 2, + 3) of 8 rows, per 128 columns
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
         for (int k = 0; k < VK; ++k)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[r][k][c] = 0.f;
+            for (int c = 0; c < 2; ++c) acc[r][k][c] = 0ull;
     const int nf = min(a.keep_first, lo);              // kept first positions before the window: a run of key tiles of their own
     for (int seg = nf > 0 ? 0 : 1; seg < 2; ++seg) {
     const int kend = seg ? hi + 1 : nf;
@@ -335,23 +354,32 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
             *reinterpret_cast<float4*>(Vs + c * ldv + 4 * d4) = v;
         }
         __syncthreads();
+        // a score is summed in two halves, even and odd channels side by side in one packed register: the 16-byte reads of
+        // queries and keys are already pairs of neighbouring channels, so every multiply-add is two-wide without a move
         float sc[2][4];
+        f32x2 sc2[2][4];
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) sc[i][c] = 0.f;
+            for (int c = 0; c < 4; ++c) sc2[i][c] = 0ull;
         for (int d4 = 0; d4 < d4n; ++d4) {
-            const float4 q0v = *reinterpret_cast<const float4*>(Qs + (2 * ry) * ldq + 4 * d4);
-            const float4 q1v = *reinterpret_cast<const float4*>(Qs + (2 * ry + 1) * ldq + 4 * d4);
+            const ulonglong2 q0v = *reinterpret_cast<const ulonglong2*>(Qs + (2 * ry) * ldq + 4 * d4);
+            const ulonglong2 q1v = *reinterpret_cast<const ulonglong2*>(Qs + (2 * ry + 1) * ldq + 4 * d4);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float4 kv = *reinterpret_cast<const float4*>(Ks + (cx + 8 * c) * ldq + 4 * d4);
-                sc[0][c] = fmaf(q0v.x, kv.x, sc[0][c]); sc[0][c] = fmaf(q0v.y, kv.y, sc[0][c]);
-                sc[0][c] = fmaf(q0v.z, kv.z, sc[0][c]); sc[0][c] = fmaf(q0v.w, kv.w, sc[0][c]);
-                sc[1][c] = fmaf(q1v.x, kv.x, sc[1][c]); sc[1][c] = fmaf(q1v.y, kv.y, sc[1][c]);
-                sc[1][c] = fmaf(q1v.z, kv.z, sc[1][c]); sc[1][c] = fmaf(q1v.w, kv.w, sc[1][c]);
+                const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(Ks + (cx + 8 * c) * ldq + 4 * d4);
+                sc2[0][c] = fma2(q0v.x, kv.x, sc2[0][c]); sc2[0][c] = fma2(q0v.y, kv.y, sc2[0][c]);
+                sc2[1][c] = fma2(q1v.x, kv.x, sc2[1][c]); sc2[1][c] = fma2(q1v.y, kv.y, sc2[1][c]);
             }
         }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float ev, od;
+                unpack2(sc2[i][c], ev, od);
+                sc[i][c] = ev + od;
+            }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             float tmax = -INFINITY;
@@ -389,25 +417,27 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             const float f = cr[8 * oy + r];
+            const f32x2 f2 = pack2(f, f);
 #pragma unroll
             for (int k = 0; k < VK; ++k)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) acc[r][k][c] *= f;
+                for (int c = 0; c < 2; ++c) acc[r][k][c] = mul2(acc[r][k][c], f2);
         }
         for (int c = 0; c < WT_KEYS; ++c) {
-            float4 vv[VK];
+            ulonglong2 vv[VK];
 #pragma unroll
             for (int k = 0; k < VK; ++k) {
                 const int col = 4 * ox + 128 * k;
-                vv[k] = col < a.vdim ? *reinterpret_cast<const float4*>(Vs + c * ldv + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+                vv[k] = col < a.vdim ? *reinterpret_cast<const ulonglong2*>(Vs + c * ldv + col) : make_ulonglong2(0ull, 0ull);
             }
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
                 const float pv = Ps[(8 * oy + r) * ldp + c];
+                const f32x2 p2 = pack2(pv, pv);
 #pragma unroll
                 for (int k = 0; k < VK; ++k) {
-                    acc[r][k][0] = fmaf(pv, vv[k].x, acc[r][k][0]); acc[r][k][1] = fmaf(pv, vv[k].y, acc[r][k][1]);
-                    acc[r][k][2] = fmaf(pv, vv[k].z, acc[r][k][2]); acc[r][k][3] = fmaf(pv, vv[k].w, acc[r][k][3]);
+                    acc[r][k][0] = fma2(p2, vv[k].x, acc[r][k][0]);
+                    acc[r][k][1] = fma2(p2, vv[k].y, acc[r][k][1]);
                 }
             }
         }
@@ -435,9 +465,12 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
 #pragma unroll
         for (int k = 0; k < VK; ++k) {
             const int col = 4 * ox + 128 * k;
-            if (col < a.vdim)
-                *reinterpret_cast<float4*>(orow + col) =
-                    make_float4(acc[r][k][0] * inv, acc[r][k][1] * inv, acc[r][k][2] * inv, acc[r][k][3] * inv);
+            if (col < a.vdim) {
+                float o0, o1, o2, o3;
+                unpack2(acc[r][k][0], o0, o1);
+                unpack2(acc[r][k][1], o2, o3);
+                *reinterpret_cast<float4*>(orow + col) = make_float4(o0 * inv, o1 * inv, o2 * inv, o3 * inv);
+            }
         }
     }
 }
@@ -506,23 +539,6 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
 constexpr int RCH = 16, RTHREADS = 128;
 // stages of the ring for a padded row of DP floats: as deep as ~100-160 KB of shared memory allow
 __host__ __device__ constexpr int rule_stages(int dp) { return 2; }
-typedef unsigned long long f32x2;      // two fp32 numbers in one 64-bit register
-__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
 template <int N> __device__ __forceinline__ void cp_async_wait_pending() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
