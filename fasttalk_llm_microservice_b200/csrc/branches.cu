@@ -154,11 +154,12 @@ __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
         a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos,
                                               a.qk_norm ? inv[i / a.dim] : 1.f);
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
-    float* row = a.cache + ((size_t)pt[p >> 6] * 64 + (p & 63)) * (size_t)(nk + nv);
+    const bool alias = a.v_in_key >= 0;                // the values are columns of the keys: the row holds the keys only
+    float* row = a.cache + ((size_t)pt[p >> 6] * 64 + (p & 63)) * (size_t)(alias ? nk : nk + nv);
     for (int i = threadIdx.x; i < nk; i += blockDim.x)
         row[i] = rotated(pr + a.o_k, a.k_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos, a.qk_norm ? inv[a.H + i / a.dim] : 1.f);
     const float lam = a.v_role == 2 ? a.v_mix[0] : 0.f;
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    for (int i = threadIdx.x; i < (alias ? 0 : nv); i += blockDim.x) {
         float v = a.o_v >= 0 ? pr[a.o_v + i] + (a.v_bias ? a.v_bias[i] : 0.f) : pr[a.o_k + i] + (a.k_bias ? a.k_bias[i] : 0.f);
         if (a.v_role == 1) a.v_first[(size_t)t * nv + i] = v;
         else if (a.v_role == 2) v = (1.f - lam) * v + lam * a.v_first[(size_t)t * nv + i];
@@ -201,7 +202,9 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     const int nf = min(a.keep_first, lo);              // kept first positions that lie before the window
     const int n = nf + p - lo + 1;                     // key idx < nf: position idx; otherwise position lo + idx - nf
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
-    const size_t rowsz = (size_t)a.G * (a.dim + a.vdim);
+    const bool alias = a.v_in_key >= 0;
+    const size_t rowsz = (size_t)a.G * (alias ? a.dim : a.dim + a.vdim);
+    const size_t v_at = alias ? (size_t)g * a.dim + a.v_in_key : (size_t)a.G * a.dim + (size_t)g * a.vdim;
     for (int c = threadIdx.x; c < a.dim; c += blockDim.x) sq[c] = a.q_out[((size_t)t * a.H + h) * a.dim + c];
     __syncthreads();
     float m = -INFINITY, l = 0.f, acc[VPL];
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
             for (int u = 0; u < 4; ++u) {
                 px[u] = __shfl_sync(0xffffffffu, pj, x0 + u);
                 const long long bx = __shfl_sync(0xffffffffu, base, x0 + u);
-                vr[u] = a.cache + bx + (size_t)a.G * a.dim + (size_t)g * a.vdim;
+                vr[u] = a.cache + bx + v_at;
             }
             float vv[4][VPL];
 #pragma unroll
@@ -294,11 +297,12 @@ constexpr int WT_ROWS = 64, WT_KEYS = 32, WT_THREADS = 256;
 template <int VK>
 __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, WindowTiles tm, int QT, int subs) {
     extern __shared__ __align__(16) float wsh[];
-    const int ldq = a.dim + 4, ldv = a.vdim, ldp = WT_KEYS + 1;
+    const bool alias = a.v_in_key >= 0;       // the values are columns v_in_key.. of the key rows: no value tile of their own
+    const int ldq = a.dim + 4, ldv = alias ? ldq : a.vdim, ldp = WT_KEYS + 1;
     float* Qs = wsh;                          // [64][dim + 4]
     float* Ks = Qs + WT_ROWS * ldq;           // [32][dim + 4]
-    float* Vs = Ks + WT_KEYS * ldq;           // [32][vdim]
-    float* Ps = Vs + WT_KEYS * ldv;           // [64][33]
+    float* Vs = alias ? Ks + a.v_in_key : Ks + WT_KEYS * ldq;      // [32][vdim]
+    float* Ps = Ks + WT_KEYS * ldq + (alias ? 0 : WT_KEYS * ldv);  // [64][33]
     float* cr = Ps + WT_ROWS * ldp;           // [64] rescale of a row's sums in this tile; at the end the row's softmax sum
     const int tile = blockIdx.x / subs, sub = blockIdx.x % subs, g = blockIdx.y, tid = threadIdx.x;
     const int j = tm.tile_req[tile];
@@ -309,8 +313,8 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
     const int row_base = tm.req_q_start[j] + q0, p_first = tm.req_pos0[j] + q0;
     const int* pt = a.page_table + (size_t)tm.req_slot[j] * a.max_pages;
     const int grp = a.H / a.G, rows_used = ntok * grp;
-    const size_t rowsz = (size_t)a.G * (a.dim + a.vdim);
-    const int d4n = a.dim >> 2, v4n = a.vdim >> 2;
+    const size_t rowsz = (size_t)a.G * (alias ? a.dim : a.dim + a.vdim);
+    const int d4n = a.dim >> 2, v4n = alias ? 0 : a.vdim >> 2;
     for (int i = tid; i < WT_ROWS * d4n; i += WT_THREADS) {
         const int r = i / d4n, d4 = i - r * d4n;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -483,15 +487,17 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
                "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
     FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0,
                "window attention: rotary pairs need even sizes (dim %d, rotated %d)", a.dim, a.rot_dims);
-    FT_REQUIRE(a.o_v >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
+    FT_REQUIRE(a.o_v >= 0 || a.v_in_key >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
     FT_REQUIRE(a.keep_first >= 0 && (!a.rel || a.rel_n >= 1) && (a.v_role == 0 || (a.v_first && a.o_v >= 0)) &&
                    (a.v_role != 2 || a.v_mix),
                "window attention: incomplete options");
     window_write_kernel<<<T, 128, a.qk_norm ? (size_t)(a.H + a.G) * 4 : 0, stream>>>(a);
     FT_CHECK_CUDA(cudaGetLastError());
     const int grp = a.H / a.G;
-    const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + WT_KEYS * a.vdim + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
-    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && a.vdim <= 256 && tsm <= 200 * 1024;
+    FT_REQUIRE(a.v_in_key < 0 || (a.v_in_key + a.vdim <= a.dim && a.v_role == 0), "window attention: values inside the keys exceed them");
+    const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + (a.v_in_key >= 0 ? 0 : WT_KEYS * a.vdim) + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
+    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && a.vdim <= 256 && tsm <= 200 * 1024 &&
+                       (a.v_in_key < 0 || (a.v_in_key & 3) == 0);
     int rows_each = T;                                 // rows of the one-CTA-per-(token, head) kernel
     if (tiled) {
         rows_each = n_single;

@@ -722,9 +722,9 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
             a.qk_norm = c.qk_norm; a.eps = M.eps; a.keep_first = c.keep_first; a.sink = c.sink; a.rel = c.rel; a.rel_n = c.rel_n;
             a.v_bias = c.v_bias; a.v_role = c.v_role; a.v_mix = c.v_mix; a.v_first = L.v_first;
         } else {
-            // One shared key head: cached key [rotated part | normed latent], value = the latent.  The plain query part is
-            // folded through W_uk into latent space, so no per-head key or value is ever formed.
-            const int H = c.heads, R = c.rot_dims, C = c.kv_rank, D = c.dim, kd = R + C, ls = H * kd + kd + C;
+            // One shared key head: cached key [rotated part | normed latent], the value is its latent part.  The plain query
+            // part is folded through W_uk into latent space, so no per-head key or value is ever formed.
+            const int H = c.heads, R = c.rot_dims, C = c.kv_rank, D = c.dim, kd = R + C, ls = H * kd + kd;
             FT_TRY(launch_rms_cols(L.proj, ld, c.o_q, c.q_norm, L.b1, c.q_rank, 0, c.q_rank, M.eps, T, st));
             FT_TRY(dense(e, L.b1, nullptr, nullptr, c.w_uq, L.b2, T, H * (D + R), c.q_rank));
             FT_TRY(launch_latent_stage(L.b2, H, D, R, L.proj, ld, c.o_k, C, c.kv_norm, M.eps, L.lstage, ls, T, st));
@@ -734,7 +734,7 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
             f.C = L.lstage + R; f.ldc = ls; f.c_col_stride = kd; f.M = T; f.N = C; f.K = D; f.P = H;
             FT_TRY(launch_linear(f, T, st));
             launched(3);
-            a.proj = L.lstage; a.ldp = ls; a.o_q = 0; a.o_k = H * kd; a.o_v = H * kd + kd;
+            a.proj = L.lstage; a.ldp = ls; a.o_q = 0; a.o_k = H * kd; a.o_v = -1; a.v_in_key = R;
             a.G = 1; a.dim = kd; a.vdim = C;
         }
         WindowTiles tm;
@@ -1589,10 +1589,10 @@ static int engine_init_layered(Engine* e) {
                                "engine: latent-window layer %d branch %d is incomplete", l, k);
                     const size_t kd = (size_t)c.rot_dims + c.kv_rank;
                     ll.br_cache_off[k] = kv_floats;
-                    kv_floats += (size_t)e->cfg.num_pages * kKvTile * (kd + c.kv_rank);
+                    kv_floats += (size_t)e->cfg.num_pages * kKvTile * kd;
                     br_q = std::max(br_q, (size_t)c.heads * kd);
                     br_fin = std::max(br_fin, (size_t)c.heads * c.kv_rank);
-                    lstage_cols = std::max(lstage_cols, (size_t)c.heads * kd + kd + c.kv_rank);
+                    lstage_cols = std::max(lstage_cols, (size_t)c.heads * kd + kd);
                     buf = std::max(buf, std::max((size_t)c.q_rank, (size_t)c.heads * (c.dim + c.rot_dims)));
                 } else if (c.kind == FT_BRANCH_DECAY_ATTENTION) {
                     FT_REQUIRE(c.kv_heads == c.heads && c.decay && c.out_norm && c.o_v >= 0 && c.o_g >= 0 &&

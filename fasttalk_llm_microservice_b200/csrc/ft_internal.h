@@ -213,6 +213,8 @@ struct WindowArgs {
     int v_role = 0;                               // 1: values also go to v_first; 2: v <- (1 - v_mix) v + v_mix v_first
     const float* v_mix = nullptr;                 // [1]
     float* v_first = nullptr;                     // [T][G * vdim] of the step
+    int v_in_key = -1;                            // >= 0: the value of a key head is columns v_in_key .. + vdim of its (rotated) key;
+                                                  // the cache row then holds the keys only
 };
 // The step's prompt portions as the batch builder lists them: 64-token query tiles (request, first token), and per request
 // its first row in the step, its page-table row and the position of its first token.
@@ -336,7 +338,7 @@ int launch_rms_rows(const float* x, const int* rows, const float* w, float gain,
 int launch_rms_cols(const float* src, int lds, int src_off, const float* w, float* dst, int ldd, int dst_off, int n, float eps,
                     int T, cudaStream_t stream);
 // Latent window attention: the staging row [heads x (rot query part | room for the folded plain query)] [rot key part |
-// normed latent] [normed latent] of every token, from the query projection q [T][heads][dim | rot] and the layer's projection
+// normed latent] of every token, from the query projection q [T][heads][dim | rot] and the layer's projection
 // (rank latent columns, then rot columns, at o_k; latent gain w)
 int launch_latent_stage(const float* q, int heads, int dim, int rot, const float* proj, int ldp, int o_k, int rank, const float* w,
                         float eps, float* stage, int lds, int T, cudaStream_t stream);

@@ -221,7 +221,7 @@ int launch_rms_cols(const float* src, int lds, int src_off, const float* w, floa
 
 // Latent window attention, per token: from the query projection q [heads][dim plain | rot] and the layer's projection
 // (kv_rank latent columns, then rot columns of the shared key part at o_k) to the staging row the window-attention kernels read:
-//   [heads x (rot query part | folded plain query, written by the caller's GEMM)] [rot key part | normed latent] [normed latent]
+//   [heads x (rot query part | folded plain query, written by the caller's GEMM)] [rot key part | normed latent]
 __global__ void __launch_bounds__(128)
 latent_stage_kernel(const float* __restrict__ q, int heads, int dim, int rot, const float* __restrict__ proj, int ldp, int o_k,
                     int rank, const float* __restrict__ w, float eps, float* __restrict__ stage, int lds) {
@@ -243,7 +243,6 @@ latent_stage_kernel(const float* __restrict__ q, int heads, int dim, int rot, co
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         const float v = pr[c] * r * w[c];
         key[rot + c] = v;
-        key[kd + c] = v;
     }
 }
 int launch_latent_stage(const float* q, int heads, int dim, int rot, const float* proj, int ldp, int o_k, int rank, const float* w,
