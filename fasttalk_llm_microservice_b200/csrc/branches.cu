@@ -186,6 +186,11 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     return r;
 }
 
+// 16-byte asynchronous copy global -> shared of which only the first src_bytes (0 or 16) are read, the rest filled with zeros
+__device__ __forceinline__ void cp_async16_zfill(float* dst_smem, const float* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(src_bytes) : "memory");
+}
+
 constexpr int kWinWarps = 4;
 template <int VPL, bool VEC>
 __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs a) {
@@ -299,10 +304,10 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
     extern __shared__ __align__(16) float wsh[];
     const bool alias = a.v_in_key >= 0;       // the values are columns v_in_key.. of the key rows: no value tile of their own
     const int ldq = a.dim + 4, ldv = alias ? ldq : a.vdim, ldp = WT_KEYS + 1;
+    const int kvf = WT_KEYS * ldq + (alias ? 0 : WT_KEYS * ldv);      // floats of one staged key (+ value) tile
     float* Qs = wsh;                          // [64][dim + 4]
-    float* Ks = Qs + WT_ROWS * ldq;           // [32][dim + 4]
-    float* Vs = alias ? Ks + a.v_in_key : Ks + WT_KEYS * ldq;      // [32][vdim]
-    float* Ps = Ks + WT_KEYS * ldq + (alias ? 0 : WT_KEYS * ldv);  // [64][33]
+    float* KV = Qs + WT_ROWS * ldq;           // two tiles of [32][dim + 4] keys (+ [32][vdim] values): one in use, one arriving
+    float* Ps = KV + 2 * kvf;                 // [64][33]
     float* cr = Ps + WT_ROWS * ldp;           // [64] rescale of a row's sums in this tile; at the end the row's softmax sum
     const int tile = blockIdx.x / subs, sub = blockIdx.x % subs, g = blockIdx.y, tid = threadIdx.x;
     const int j = tm.tile_req[tile];
@@ -337,27 +342,37 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
         for (int k = 0; k < VK; ++k)
 #pragma unroll
             for (int c = 0; c < 2; ++c) acc[r][k][c] = 0ull;
-    const int nf = min(a.keep_first, lo);              // kept first positions before the window: a run of key tiles of their own
-    for (int seg = nf > 0 ? 0 : 1; seg < 2; ++seg) {
-    const int kend = seg ? hi + 1 : nf;
-    for (int k0 = seg ? lo : 0; k0 < kend; k0 += WT_KEYS) {
-        __syncthreads();                               // the last tile's sums are done with Ks / Vs / Ps
+    // The key tiles of this CTA in order: first those of the kept first positions that lie before the window (keys below nf),
+    // then those of the window up to the run's last position.  Tile it + 1 is copied asynchronously while tile it is used.
+    const int nf = min(a.keep_first, lo);
+    const int n0 = (nf + WT_KEYS - 1) / WT_KEYS, nt = n0 + (hi - lo) / WT_KEYS + 1;
+    auto stage = [&](int it, float* buf) {
+        const bool seg = it >= n0;
+        const int k0 = seg ? lo + (it - n0) * WT_KEYS : it * WT_KEYS, kend = seg ? hi + 1 : nf;
         for (int i = tid; i < WT_KEYS * d4n; i += WT_THREADS) {
             const int c = i / d4n, d4 = i - c * d4n, key = k0 + c;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (key < kend)
-                v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)g * a.dim + 4 * d4);
-            *reinterpret_cast<float4*>(Ks + c * ldq + 4 * d4) = v;
+            const bool ok = key < kend;             // rows beyond the end are filled with zeros (a copy of no source bytes)
+            const float* src = ok ? a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)g * a.dim + 4 * d4 : a.cache;
+            cp_async16_zfill(buf + c * ldq + 4 * d4, src, ok ? 16 : 0);
         }
         for (int i = tid; i < WT_KEYS * v4n; i += WT_THREADS) {
             const int c = i / v4n, d4 = i - c * v4n, key = k0 + c;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (key < kend)
-                v = *reinterpret_cast<const float4*>(a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)a.G * a.dim +
-                                                     (size_t)g * a.vdim + 4 * d4);
-            *reinterpret_cast<float4*>(Vs + c * ldv + 4 * d4) = v;
+            const bool ok = key < kend;
+            const float* src = ok ? a.cache + ((size_t)pt[key >> 6] * 64 + (key & 63)) * rowsz + (size_t)a.G * a.dim + (size_t)g * a.vdim + 4 * d4
+                                  : a.cache;
+            cp_async16_zfill(buf + WT_KEYS * ldq + c * ldv + 4 * d4, src, ok ? 16 : 0);
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, KV);
+    for (int it = 0; it < nt; ++it) {
+        const bool seg = it >= n0;
+        const int k0 = seg ? lo + (it - n0) * WT_KEYS : it * WT_KEYS, kend = seg ? hi + 1 : nf;
+        const float* Ks = KV + (it & 1) * kvf;
+        const float* Vs = alias ? Ks + a.v_in_key : Ks + WT_KEYS * ldq;
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();                               // tile `it` has landed; the last tile's sums are done with the other buffer and Ps
+        if (it + 1 < nt) stage(it + 1, KV + ((it + 1) & 1) * kvf);
         // a score is summed in two halves, even and odd channels side by side in one packed register: the 16-byte reads of
         // queries and keys are already pairs of neighbouring channels, so every multiply-add is two-wide without a move
         float sc[2][4];
@@ -446,7 +461,6 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
             }
         }
     }
-    }
     __syncthreads();
     if (cx == 0) {                                     // per row: what its sums are multiplied by at the end
 #pragma unroll
@@ -495,8 +509,8 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
     FT_CHECK_CUDA(cudaGetLastError());
     const int grp = a.H / a.G;
     FT_REQUIRE(a.v_in_key < 0 || (a.v_in_key + a.vdim <= a.dim && a.v_role == 0), "window attention: values inside the keys exceed them");
-    const size_t tsm = (size_t)((WT_ROWS + WT_KEYS) * (a.dim + 4) + (a.v_in_key >= 0 ? 0 : WT_KEYS * a.vdim) + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
-    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && a.vdim <= 256 && tsm <= 200 * 1024 &&
+    const size_t tsm = (size_t)((WT_ROWS + 2 * WT_KEYS) * (a.dim + 4) + (a.v_in_key >= 0 ? 0 : 2 * WT_KEYS * a.vdim) + WT_ROWS * (WT_KEYS + 1) + WT_ROWS) * 4;
+    const bool tiled = tm.n_tiles > 0 && (a.dim & 3) == 0 && (a.vdim & 3) == 0 && grp <= WT_ROWS && a.vdim <= 256 && tsm <= 220 * 1024 &&
                        (a.v_in_key < 0 || (a.v_in_key & 3) == 0);
     int rows_each = T;                                 // rows of the one-CTA-per-(token, head) kernel
     if (tiled) {
