@@ -78,11 +78,14 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
     const float* A = a.A + (size_t)p * a.a_col_stride;
     const __nv_bfloat16* W = a.W + (size_t)p * a.w_stride;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // 16 x 16 threads, 4 x 4 outputs each
-    float acc[4][4];
+    // Every output is summed in two levels: the LBK products of a K tile in one short chain, the tiles' sums with a running
+    // compensation term (the rounding error of each addition is carried into the next), so the result's error does not grow
+    // with K as one long chain of multiply-adds would.
+    float acc[4][4], comp[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = comp[i][j] = 0.f;
     // loader mapping: thread -> (row within tile, 4 consecutive k)
     const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;
     const int arow_t = row0 + lr;
@@ -116,6 +119,11 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) { sA[lk + i][lr] = av[i]; sW[lk + i][lr] = wv[i]; }
         __syncthreads();
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < LBK; ++kk) {
             const float4 x = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
@@ -124,8 +132,17 @@ __global__ void __launch_bounds__(LTHREADS) linear_tile_kernel(LinearArgs a) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(xa[i], wa[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float y = part[i][j] - comp[i][j];
+                const float t = __fadd_rn(acc[i][j], y);
+                comp[i][j] = __fadd_rn(__fadd_rn(t, -acc[i][j]), -y);
+                acc[i][j] = t;
+            }
     }
     float* C = a.C + (size_t)p * a.c_col_stride;
 #pragma unroll
