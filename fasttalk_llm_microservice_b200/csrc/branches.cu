@@ -6,7 +6,10 @@
 //                        the experts' weighted sum plus the shared expert): one kernel between any two GEMMs of a layer
 //   window attention     biases + rotary pairs, rotated keys and values into the paged cache; one CTA per (token, head),
 //                        its warps take key blocks of the window in turn (one key per lane for the scores, one value column
-//                        per lane for the sum), online softmax, merged through shared memory
+//                        per lane for the sum), online softmax, merged through shared memory; prompt portions on a tiled
+//                        kernel.  Options, each off by default: queries and keys divided by their root mean square, a bias
+//                        by distance, first positions that stay visible beyond the window, a sink in the softmax denominator,
+//                        values mixed with those an earlier layer kept for the step, values that are columns of the keys
 //   scalar-decay rule    S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t for a request's tokens in order; one CTA per (request,
 //                        head, block of value columns), LPC lanes share a column and hold a run of key channels of its
 //                        state in registers.  Decay attention, the gated matrix memory and the state-space mixer all run
