@@ -120,15 +120,26 @@ int launch_const_decay(const float* decay, float* ab, int heads, int T, cudaStre
 // ------------------------------------------------------------------ window attention
 // Token t: q = proj[o_q ..] + bias, rotated, -> q_out; k = proj[o_k ..] + bias: the rotated key and the value (the key before
 // rotation, or proj[o_v ..]) -> the cache row of its position: [kv_heads * dim keys | kv_heads * vdim values].
-__device__ __forceinline__ float rotated(const float* __restrict__ src, const float* __restrict__ bias, int idx, int c,
-                                         int rot_dims, const float* __restrict__ freq, float pos, float sc) {
-    const float me = (src[idx] + (bias ? bias[idx] : 0.f)) * sc;
-    if (c >= rot_dims) return me;
-    const int other = (c & 1) ? idx - 1 : idx + 1;      // (2i, 2i+1) pairs inside the head
-    const float ot = (src[other] + (bias ? bias[other] : 0.f)) * sc;
+// One coordinate of a query or key head after bias, norm factor, gain and rotation.  idx: its place in the projection's run of
+// heads; c: its place inside the head; gi0: where the head's gains start in `gain` (the same for all heads, or per head).
+struct RotSpec { const float* freq; int dims, half_layout; float mag; };
+__device__ __forceinline__ float rotated(const float* __restrict__ src, const float* __restrict__ bias, const float* __restrict__ gain,
+                                         int gi0, int idx, int c, const RotSpec& r, float pos, float sc) {
+    float me = (src[idx] + (bias ? bias[idx] : 0.f)) * sc;
+    if (gain) me *= gain[gi0 + c];
+    if (c >= r.dims) return me;
+    const int half = r.dims >> 1;
+    // partner and turning direction: (2i, 2i+1) pairs, or (i, i + dims / 2)
+    const bool second = r.half_layout ? c >= half : (c & 1);
+    const int oc = r.half_layout ? (second ? c - half : c + half) : (second ? c - 1 : c + 1);
+    const int other = idx + (oc - c);
+    float ot = (src[other] + (bias ? bias[other] : 0.f)) * sc;
+    if (gain) ot *= gain[gi0 + oc];
     float sn, cs;
-    sincosf(pos * freq[c >> 1], &sn, &cs);
-    return (c & 1) ? me * cs + ot * sn : me * cs - ot * sn;
+    sincosf(pos * r.freq[r.half_layout ? (second ? c - half : c) : (c >> 1)], &sn, &cs);
+    sn *= r.mag;
+    cs *= r.mag;
+    return second ? me * cs + ot * sn : me * cs - ot * sn;
 }
 __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
     extern __shared__ float inv[];             // qk_norm: 1 / rms of every query head, then of every key head
@@ -137,9 +148,27 @@ __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
     const int p = a.positions[t];
     const float pos = (float)p;
     const int nq = a.H * a.dim, nk = a.G * a.dim, nv = a.G * a.vdim;
-    if (a.qk_norm) {
+    const int nkh = a.no_kv ? 0 : a.G;            // key heads this layer forms itself
+    if (a.qk_norm == 2) {
+        // one root mean square over all heads of q, one over all heads of k
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        if (wid < 2 && (wid == 0 || nkh > 0)) {
+            const float* src = pr + (wid == 0 ? a.o_q : a.o_k);
+            const float* bias = wid == 0 ? a.q_bias : a.k_bias;
+            const int n = wid == 0 ? nq : nk;
+            float ss = 0.f;
+            for (int d = lane; d < n; d += 32) {
+                const float v = src[d] + (bias ? bias[d] : 0.f);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            const float r = 1.f / sqrtf(ss / (float)n + a.eps);
+            for (int hh = lane; hh < (wid == 0 ? a.H : a.G); hh += 32) inv[(wid == 0 ? 0 : a.H) + hh] = r;
+        }
+        __syncthreads();
+    } else if (a.qk_norm) {
         const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-        for (int hh = wid; hh < a.H + a.G; hh += nw) {
+        for (int hh = wid; hh < a.H + nkh; hh += nw) {
             const bool isq = hh < a.H;
             const float* src = pr + (isq ? a.o_q + hh * a.dim : a.o_k + (hh - a.H) * a.dim);
             const float* bias = isq ? (a.q_bias ? a.q_bias + hh * a.dim : nullptr) : (a.k_bias ? a.k_bias + (hh - a.H) * a.dim : nullptr);
@@ -153,14 +182,18 @@ __global__ void __launch_bounds__(128) window_write_kernel(WindowArgs a) {
         }
         __syncthreads();
     }
+    const RotSpec rs = {a.rot_freq, a.rot_dims, a.rot_half, a.rot_mag};
+    const bool wide = a.qk_norm == 2;             // gains per (head, coordinate) instead of per coordinate
     for (int i = threadIdx.x; i < nq; i += blockDim.x)
-        a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos,
+        a.q_out[(size_t)t * nq + i] = rotated(pr + a.o_q, a.q_bias, a.q_gain, wide ? i - i % a.dim : 0, i, i % a.dim, rs, pos,
                                               a.qk_norm ? inv[i / a.dim] : 1.f);
+    if (a.no_kv) return;
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
     const bool alias = a.v_in_key >= 0;                // the values are columns of the keys: the row holds the keys only
     float* row = a.cache + ((size_t)pt[p >> 6] * 64 + (p & 63)) * (size_t)(alias ? nk : nk + nv);
     for (int i = threadIdx.x; i < nk; i += blockDim.x)
-        row[i] = rotated(pr + a.o_k, a.k_bias, i, i % a.dim, a.rot_dims, a.rot_freq, pos, a.qk_norm ? inv[a.H + i / a.dim] : 1.f);
+        row[i] = rotated(pr + a.o_k, a.k_bias, a.k_gain, wide ? i - i % a.dim : 0, i, i % a.dim, rs, pos,
+                         a.qk_norm ? inv[a.H + i / a.dim] : 1.f);
     const float lam = a.v_role == 2 ? a.v_mix[0] : 0.f;
     for (int i = threadIdx.x; i < (alias ? 0 : nv); i += blockDim.x) {
         float v = a.o_v >= 0 ? pr[a.o_v + i] + (a.v_bias ? a.v_bias[i] : 0.f) : pr[a.o_k + i] + (a.k_bias ? a.k_bias[i] : 0.f);
@@ -206,7 +239,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attn_kernel(WindowArgs 
     const int g = h / (a.H / a.G);
     const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = a.positions[t];
-    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int lo = a.window > 0 ? (a.chunked ? p - p % a.window : max(0, p - a.window + 1)) : 0;
     const int nf = min(a.keep_first, lo);              // kept first positions that lie before the window
     const int n = nf + p - lo + 1;                     // key idx < nf: position idx; otherwise position lo + idx - nf
     const int* pt = a.page_table + (size_t)a.seq_rows[t] * a.max_pages;
@@ -330,7 +363,7 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
             v = *reinterpret_cast<const float4*>(a.q_out + ((size_t)(row_base + r / grp) * a.H + g * grp + r % grp) * a.dim + 4 * d4);
         *reinterpret_cast<float4*>(Qs + r * ldq + 4 * d4) = v;
     }
-    const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0, hi = p_first + ntok - 1;
+    const int lo = a.window > 0 ? (a.chunked ? p_first - p_first % a.window : max(0, p_first - a.window + 1)) : 0, hi = p_first + ntok - 1;
     const int ry = tid >> 3, cx = tid & 7;            // scores: rows 2 ry, 2 ry + 1; keys cx, cx + 8, cx + 16, cx + 24 of the tile
     const int oy = tid >> 5, ox = tid & 31;           // sums: rows 8 oy .. 8 oy + 7; columns 4 ox .. 4 ox + 3 (+ 128)
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -410,7 +443,8 @@ __global__ void __launch_bounds__(WT_THREADS) window_tile_kernel(WindowArgs a, W
                 const int key = k0 + cx + 8 * c;
                 float v = sc[i][c] * a.scale;
                 if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-                const bool vis = rv[i] && key < kend && key <= pr[i] && (a.window <= 0 || key > pr[i] - a.window || key < a.keep_first);
+                const bool vis = rv[i] && key < kend && key <= pr[i] &&
+                                 (a.window <= 0 || (a.chunked ? key >= pr[i] - pr[i] % a.window : key > pr[i] - a.window) || key < a.keep_first);
                 if (a.rel && vis) v += a.rel[(size_t)min(pr[i] - key, a.rel_n - 1) * a.H + g * grp + (2 * ry + i) % grp];
                 sc[i][c] = vis ? v : -INFINITY;
                 tmax = fmaxf(tmax, sc[i][c]);
@@ -504,7 +538,8 @@ int launch_window_attention(const WindowArgs& a, int T, int n_single, const Wind
                "window attention: bad head sizes (heads %d, kv heads %d, dim %d, vdim %d)", a.H, a.G, a.dim, a.vdim);
     FT_REQUIRE(a.rot_dims >= 0 && a.rot_dims <= a.dim && (a.rot_dims & 1) == 0,
                "window attention: rotary pairs need even sizes (dim %d, rotated %d)", a.dim, a.rot_dims);
-    FT_REQUIRE(a.o_v >= 0 || a.v_in_key >= 0 || a.vdim == a.dim, "window attention: keys used as values need vdim == dim");
+    FT_REQUIRE(a.o_v >= 0 || a.v_in_key >= 0 || a.vdim == a.dim || a.no_kv, "window attention: keys used as values need vdim == dim");
+    FT_REQUIRE(a.qk_norm >= 0 && a.qk_norm <= 2 && (!a.chunked || a.window > 0), "window attention: bad norm or chunk options");
     FT_REQUIRE(a.keep_first >= 0 && (!a.rel || a.rel_n >= 1) && (a.v_role == 0 || (a.v_first && a.o_v >= 0)) &&
                    (a.v_role != 2 || a.v_mix),
                "window attention: incomplete options");
@@ -913,7 +948,7 @@ __global__ void __launch_bounds__(256) space_conv_kernel(SpaceArgs a) {
             else if (pos0 + k - j >= 0) u = tail[(size_t)c * (K - 1) + (k - j + K - 1)];
             acc = fmaf(a.conv_w[(size_t)c * K + (K - 1 - j)], u, acc);
         }
-        a.xbc[(size_t)t * a.channels + c] = silu_f(acc);
+        a.xbc[(size_t)t * a.channels + c] = a.act ? silu_f(acc) : acc;
     }
     for (int h = threadIdx.x; h < a.heads; h += blockDim.x) {
         const float dt = softplus_f(a.proj[(size_t)t * a.ldp + a.o_dt + h] + a.dt_bias[h]);

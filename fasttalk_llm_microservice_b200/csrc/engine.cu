@@ -173,6 +173,7 @@ struct LayeredLayer {
     // there (the running maximum of a matrix memory, the convolution tails of a state space)
     size_t br_cache_off[2] = {0, 0}, br_s_off[2] = {0, 0}, br_x_off[2] = {0, 0};
     size_t canon_off[2] = {0, 0};      // post-norm layers: the tails [taps - 1][width] of the two input convolutions in a slot
+    int lender_branch[2] = {0, 0};     // window attention over another layer's cache: which branch of that layer owns it
 };
 struct Layered {
     ft_layered_model m;
@@ -209,6 +210,9 @@ struct Layered {
     // neighbouring rows of the old stream while it writes the new one)
     float *hist = nullptr, *v_first = nullptr, *lstage = nullptr, *resid2 = nullptr;
     bool postnorm = false;
+    // hyper-connected layers: the streams of a step [t_max][streams][width]
+    float* streams = nullptr;
+    bool hyper = false;
     float* trail = nullptr;            // debug: residual stream after every layer [n_layers][t_max][width]
     bool trail_on = false;
 };
@@ -607,9 +611,10 @@ static int run_experts(Engine* e, const ft_layer_desc& c, const float* logits, i
     const int W = L.m.width;
     cudaStream_t st = e->stream;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
-    const bool sandwich = c.form == FT_LAYER_SANDWICH;
+    const bool sandwich = c.form == FT_LAYER_SANDWICH || c.form == FT_LAYER_HYPER;      // forms whose router is a matrix of its own
     const int act = sandwich ? c.ff_act : FT_ACT_SWIGLU;
     const int n_up = act == FT_ACT_SWIGLU ? 2 * c.ff : c.ff;          // rows of an expert's first matrix
+    const bool scaled_in = c.route_input != 0;                        // the experts read score * row, in sorted order
     const int top = c.top;
     FT_TRY(launch_route(logits, ldl, o_router, c.experts, c.top, sandwich ? 1 : c.groups, sandwich ? 1 : c.keep, L.ids, L.wts,
                         L.seg, L.slot_token, L.slot_pos, T, st, sandwich ? c.route_kind : FT_ROUTE_SOFTMAX,
@@ -621,7 +626,8 @@ static int run_experts(Engine* e, const ft_layer_desc& c, const float* logits, i
         // One tcgen05 GEMM per expert over its run of sorted rows.  The launches need the run lengths on the host:
         // a copy of E + 1 integers and a wait, a few microseconds against the milliseconds of such a step.
         FT_CHECK_CUDA(cudaMemcpyAsync(L.h_seg, L.seg, (size_t)(c.experts + 1) * 4, cudaMemcpyDeviceToHost, st));
-        FT_TRY(launch_gather_planes_rows(L.hn, L.slot_token, L.mx_hi, L.mx_lo, pairs, W, st));
+        if (scaled_in) FT_TRY(launch_scaled_rows(L.hn, L.wts, L.slot_pos, top, nullptr, L.mx_hi, L.mx_lo, pairs, W, st));
+        else FT_TRY(launch_gather_planes_rows(L.hn, L.slot_token, L.mx_hi, L.mx_lo, pairs, W, st));
         FT_CHECK_CUDA(cudaStreamSynchronize(st));
         auto off = [](const void* p, size_t elems) { return (const void*)((const uint8_t*)p + elems * 2); };
         ft_gemm_epilogue ep = {};
@@ -663,6 +669,11 @@ static int run_experts(Engine* e, const ft_layer_desc& c, const float* logits, i
     } else {
         LinearArgs gu;                  // first matrix of every (token, choice) pair, grouped by expert, with its activation
         gu.A = L.hn; gu.a_rows = L.slot_token; gu.lda = W; gu.W = (const __nv_bfloat16*)c.w_gu;
+        if (scaled_in) {                // the scaled rows wait in L.eout, which the second matrix overwrites afterwards
+            FT_TRY(launch_scaled_rows(L.hn, L.wts, L.slot_pos, top, L.eout, nullptr, nullptr, pairs, W, st));
+            launched();
+            gu.A = L.eout; gu.a_rows = nullptr;
+        }
         gu.w_stride = (long long)n_up * W; gu.ldw = W; gu.C = L.act; gu.ldc = c.ff; gu.seg = L.seg;
         gu.N = n_up; gu.K = W; gu.P = c.experts; gu.epi = act == FT_ACT_SWIGLU ? LIN_SWIGLU_PAIR : LIN_RELU2;
         FT_TRY(launch_linear(gu, T * top, st));
@@ -717,6 +728,25 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         a.out = L.bfin; a.H = c.heads;
         if (c.kind == FT_BRANCH_WINDOW_ATTENTION) {
             a.proj = L.proj; a.ldp = ld; a.o_q = c.o_q; a.o_k = c.o_k; a.o_v = c.o_v;
+            a.q_gain = c.q_gain; a.k_gain = c.k_gain; a.rot_half = c.rot_half; a.rot_mag = c.rot_mag != 0.f ? c.rot_mag : 1.f;
+            a.chunked = c.chunked;
+            if (c.kv_lender > 0) {          // another layer's keys and values: it has written the step's rows already
+                a.cache = L.kv_cache + L.layers[c.kv_lender - 1].br_cache_off[ll.lender_branch[k]];
+                a.no_kv = 1;
+            }
+            if (c.conv >= 1) {
+                // q | k | v through their short convolutions over time (no bias, no activation) into L.bv; the slot keeps the
+                // last projected rows
+                const int nq = c.heads * c.dim, nk = c.kv_lender > 0 ? 0 : c.kv_heads * c.dim, nv = c.kv_lender > 0 ? 0 : c.kv_heads * c.vdim;
+                SpaceArgs s;
+                s.proj = L.proj; s.ldp = ld; s.o_x = c.o_q; s.channels = nq + nk + nv; s.taps = c.conv; s.heads = 0; s.act = 0;
+                s.conv_w = c.conv_w; s.xbc = L.bv; s.state = L.state; s.slot_stride = (long long)L.slot_stride;
+                s.tail_off = (long long)ll.br_x_off[k];
+                s.seq_rows = d + m.o_rows; s.req_start = d + m.o_xstart; s.req_pos0 = d + m.o_xpos0; s.req_slot = d + m.o_xslot;
+                FT_TRY(launch_space_prep(s, T, b.n_req, st));
+                launched(2);
+                a.proj = L.bv; a.ldp = s.channels; a.o_q = 0; a.o_k = nq; a.o_v = nq + nk;
+            }
             a.q_bias = c.q_bias; a.k_bias = c.k_bias;
             a.G = c.kv_heads; a.dim = c.dim; a.vdim = c.vdim;
             a.qk_norm = c.qk_norm; a.eps = M.eps; a.keep_first = c.keep_first; a.sink = c.sink; a.rel = c.rel; a.rel_n = c.rel_n;
@@ -752,6 +782,29 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
             launched();
             fin = L.b3;
         }
+    } else if (c.kind == FT_BRANCH_SELECTIVE_SCAN) {
+        // x through its convolution (bias, SiLU) -> (low | B | C) = W_x x -> dt_raw = W_dt low -> the scan, gated by silu(z)
+        const int inner = c.heads, N = c.dim, R = c.dt_rank, nl = R + 2 * N;
+        SpaceArgs s;
+        s.proj = L.proj; s.ldp = ld; s.o_x = c.o_v; s.channels = inner; s.taps = c.conv; s.heads = 0; s.act = 1;
+        s.conv_w = c.conv_w; s.conv_b = c.conv_b; s.xbc = L.bv; s.state = L.state; s.slot_stride = (long long)L.slot_stride;
+        s.tail_off = (long long)ll.br_x_off[k];
+        s.seq_rows = d + m.o_rows; s.req_start = d + m.o_xstart; s.req_pos0 = d + m.o_xpos0; s.req_slot = d + m.o_xslot;
+        FT_TRY(launch_space_prep(s, T, b.n_req, st));
+        launched(2);
+        FT_TRY(dense(e, L.bv, nullptr, nullptr, c.w_x, L.b1, T, nl, inner));
+        LinearArgs dtp;                     // the step sizes' pre-activation from the first R columns of the low-rank row
+        dtp.A = L.b1; dtp.lda = nl; dtp.W = (const __nv_bfloat16*)c.w_dt; dtp.ldw = R; dtp.C = L.b2; dtp.ldc = inner;
+        dtp.M = T; dtp.N = inner; dtp.K = R;
+        FT_TRY(launch_linear(dtp, T, st));
+        ScanArgs sc;
+        sc.x = L.bv; sc.ldx = inner; sc.dt_raw = L.b2; sc.ldd = inner; sc.B = L.b1 + R; sc.C = L.b1 + R + N; sc.ldbc = nl;
+        sc.z = L.proj + c.o_z; sc.ldz = ld; sc.dt_bias = c.dt_bias; sc.a_log = c.a_log; sc.skip = c.skip; sc.out = L.bfin;
+        sc.state = L.state; sc.slot_stride = (long long)L.slot_stride; sc.s_off = (long long)ll.br_s_off[k];
+        sc.req_start = d + m.o_xstart; sc.req_pos0 = d + m.o_xpos0; sc.req_slot = d + m.o_xslot;
+        sc.channels = inner; sc.N = N;
+        FT_TRY(launch_selective_scan(sc, b.n_req, st));
+        launched(2);
     } else {
         RecurArgs r;
         r.ab = L.ab; r.o = L.bo; r.state = L.state; r.slot_stride = (long long)L.slot_stride; r.s_off = (long long)ll.br_s_off[k];
@@ -813,7 +866,19 @@ static int forward_layered(Engine* e, const Batch& b) {
     void* hn_hi = L.tensor && T >= kTensorMinRows ? L.hn_hi : nullptr;      // planes of the normed input, written by its producer
     void* hn_lo = hn_hi ? L.hn_lo : nullptr;
     auto launched = [&](int n = 1) { e->st.kernel_launches += n; };
-    if (L.postnorm)
+    const int n_streams = std::max(M.streams, 1);
+    const bool trail = L.trail_on && L.trail;
+    auto hyper_next = [&](HyperArgs& h, const float* in_next, const float* nw, const float* nb) {
+        h.X = L.streams; h.S = n_streams; h.W = W; h.eps = M.eps;
+        h.in_next = in_next; h.nw = nw; h.nb = nb; h.hn = L.hn; h.hi = hn_hi; h.lo = hn_lo;
+    };
+    if (L.hyper) {
+        HyperArgs h;
+        const ft_layer_desc& c0 = L.layers[0].d;
+        hyper_next(h, c0.hc_in[0], c0.norm_pre1, c0.norm_pre1_b);
+        h.tokens = d + m.o_tokens; h.embed = M.embed; h.embed_scale = M.embed_scale != 0.f ? M.embed_scale : 1.f;
+        FT_TRY(launch_hyper_joint(h, T, st));
+    } else if (L.postnorm)
         FT_TRY(launch_embed_scale(d + m.o_tokens, M.embed, M.embed_scale != 0.f ? M.embed_scale : 1.f, e->resid, L.hist, T, W, st));
     else
         FT_TRY(launch_embed_norm(d + m.o_tokens, M.embed, e->resid, L.hn, hn_hi, hn_lo, T, W, M.eps, L.layers[0].d.norm_gain,
@@ -909,7 +974,43 @@ static int forward_layered(Engine* e, const Batch& b) {
         // gains of the norm that the next layer (or the head) reads: one number, or one per coordinate
         const float gain_next = nx ? nx->norm_gain : M.final_norm_gain;
         const float* gain_next_w = nx ? (nx->form == FT_LAYER_SANDWICH ? nx->norm_pre1 : nullptr) : M.final_norm_w;
-        if (c.form == FT_LAYER_POSTNORM) {
+        if (c.form == FT_LAYER_HYPER) {
+            // every stream is rebuilt from the old ones and the sublayer's result; the same kernel forms what reads them next
+            const bool has_ff = c.ff_kind != FT_FF_NONE;
+            const float* in_after = nx ? nx->hc_in[0] : nullptr;          // the head reads the plain sum
+            const float* nw_after = nx ? nx->norm_pre1 : M.final_norm_w;
+            const float* nb_after = nx ? nx->norm_pre1_b : M.final_norm_b;
+            HyperArgs h1;
+            if (has_ff) hyper_next(h1, c.hc_in[1], c.norm_pre2, c.norm_pre2_b);
+            else hyper_next(h1, in_after, nw_after, nb_after);
+            h1.y0 = y0; h1.y1 = y1; h1.s0 = s0; h1.s1 = s1; h1.mix = c.hc_mix[0]; h1.out = c.hc_out[0];
+            if (c.mixer == FT_MIXER_BRANCHES) { h1.g0 = c.branch[0].out_gain; h1.g1 = y1 ? c.branch[1].out_gain : nullptr; }
+            if (!has_ff && trail) h1.sum_out = e->resid;
+            FT_TRY(launch_hyper_joint(h1, T, st));
+            launched();
+            if (has_ff) {
+                HyperArgs h2;
+                hyper_next(h2, in_after, nw_after, nb_after);
+                h2.mix = c.hc_mix[1]; h2.out = c.hc_out[1];
+                if (c.ff_kind == FT_FF_DENSE) {
+                    FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_gu, c.w_down, c.ff, c.ff_act, L.mix, T));
+                    h2.y0 = L.mix;
+                } else {
+                    const int ldl = c.router_rows > 0 ? c.router_rows : c.experts;
+                    FT_TRY(dense(e, L.hn, hn_hi, hn_lo, c.w_router, L.rlog, T, ldl, W));
+                    FT_TRY(run_experts(e, c, L.rlog, ldl, 0, T));
+                    h2.eout = L.eout; h2.slot_pos = L.slot_pos; h2.top = c.top;
+                    h2.wt = c.route_input ? nullptr : L.wts;
+                    if (c.shared_ff > 0) {
+                        FT_TRY(run_mlp(e, hn_hi, hn_lo, c.w_shared_up, c.w_shared_down, c.shared_ff, c.ff_act, L.mix, T));
+                        h2.y0 = L.mix;
+                    }
+                }
+                if (trail) h2.sum_out = e->resid;
+                FT_TRY(launch_hyper_joint(h2, T, st));
+                launched();
+            }
+        } else if (c.form == FT_LAYER_POSTNORM) {
             // x += norm(mixer);  x += norm(ff(x + conv(x)));  the layer's result joins the depth history and the stream that
             // goes on is the weighted sum over it
             // One kernel per joint: it also keeps the rows the sublayer read for the next step's convolution and forms what
@@ -1002,7 +1103,7 @@ static int forward_layered(Engine* e, const Batch& b) {
             FT_CHECK_CUDA(cudaMemcpyAsync(L.trail + (size_t)l * e->t_max * W, e->resid, (size_t)T * W * 4,
                                           cudaMemcpyDeviceToDevice, st));
     }
-    if (b.n_logit_rows > 0 && L.postnorm) {
+    if (b.n_logit_rows > 0 && L.postnorm && !L.hyper) {
         // the model's norm over the wanted rows only, then the head
         FT_TRY(launch_rms_rows(e->resid, b.logit_rows_identity ? nullptr : d + m.o_lrow, M.final_norm_w, M.final_norm_gain, L.xlast,
                                b.n_logit_rows, W, M.eps, st));
@@ -1529,10 +1630,18 @@ static int engine_init_layered(Engine* e) {
         LayeredLayer& ll = L.layers[l];
         const ft_layer_desc& d = ll.d;
         FT_REQUIRE(d.n_in >= 1 && d.w_in, "engine: layer %d is incomplete", l);
-        const bool sandwich = d.form == FT_LAYER_SANDWICH;
+        const bool hyper = d.form == FT_LAYER_HYPER;
+        const bool sandwich = d.form == FT_LAYER_SANDWICH || hyper;      // forms whose feed-forward has projections of its own
         const bool post = d.form == FT_LAYER_POSTNORM;
         FT_REQUIRE(post == (L.layers[0].d.form == FT_LAYER_POSTNORM), "engine: post-norm layers do not mix with other layer forms");
-        if (post) {
+        FT_REQUIRE(hyper == (L.layers[0].d.form == FT_LAYER_HYPER), "engine: hyper-connected layers do not mix with other layer forms");
+        if (hyper) {
+            FT_REQUIRE(d.norm_pre1 && (d.ff_kind == FT_FF_NONE || d.norm_pre2), "engine: hyper-connected layer %d lacks norm gains", l);
+            FT_REQUIRE(M.streams <= 16 && M.final_norm_w, "engine: a hyper-connected model has 1 to 16 streams and a last norm with gains");
+            FT_REQUIRE(d.mixer == FT_MIXER_BRANCHES || (d.mixer == FT_MIXER_CHANNEL_DELTA && d.rank_a == 0 && d.rank_g == 0),
+                       "engine: hyper-connected layer %d takes branch mixers or the delta rule with one decay per head", l);
+            L.hyper = true;
+        } else if (post) {
             FT_REQUIRE(d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.ff_kind == FT_FF_DENSE && d.norm_post2)),
                        "engine: post-norm layer %d lacks norm gains (its feed-forward is dense or absent)", l);
             FT_REQUIRE(d.canon_taps >= 0 && d.canon_taps <= 17 && (d.canon_taps == 0 || (d.canon1 && (d.ff_kind == FT_FF_NONE || d.canon2))),
@@ -1547,7 +1656,7 @@ static int engine_init_layered(Engine* e) {
                 L.n_stateful++;
             }
             if (d.depth_w) use_hist = true;
-        } else if (sandwich) {
+        } else if (d.form == FT_LAYER_SANDWICH) {
             FT_REQUIRE(d.norm_pre1 && d.norm_post1 && (d.ff_kind == FT_FF_NONE || (d.norm_pre2 && d.norm_post2)),
                        "engine: sandwich layer %d lacks norm gains", l);
         } else {
@@ -1565,7 +1674,7 @@ static int engine_init_layered(Engine* e) {
             for (int k = 0; k < d.n_branches; ++k) {
                 const ft_branch_desc& c = d.branch[k];
                 FT_REQUIRE(c.heads >= 1 && c.kv_heads >= 1 && c.heads % c.kv_heads == 0 && c.dim >= 1 && c.vdim >= 1 && c.w_o &&
-                               c.o_q >= 0 && c.o_k >= 0,
+                               (c.kind == FT_BRANCH_SELECTIVE_SCAN || (c.o_q >= 0 && (c.o_k >= 0 || c.kv_lender > 0))),
                            "engine: layer %d branch %d is incomplete", l, k);
                 const size_t hv = (size_t)c.heads * c.vdim;
                 br_heads = std::max(br_heads, (size_t)c.heads);
@@ -1574,8 +1683,34 @@ static int engine_init_layered(Engine* e) {
                     FT_REQUIRE(c.window >= 0 && (c.rot_dims == 0 || c.rot_freq), "engine: layer %d branch %d: bad window or rotation", l, k);
                     FT_REQUIRE(c.keep_first >= 0 && (!c.rel || c.rel_n >= 1) && (c.v_role == 0 || c.o_v >= 0) && (c.v_role != 2 || c.v_mix),
                                "engine: layer %d branch %d: incomplete attention options", l, k);
-                    ll.br_cache_off[k] = kv_floats;
-                    kv_floats += (size_t)e->cfg.num_pages * kKvTile * c.kv_heads * (c.dim + c.vdim);
+                    FT_REQUIRE(c.qk_norm >= 0 && c.qk_norm <= 2 && (!c.chunked || c.window > 0) && c.conv >= 0 && c.conv <= 16 &&
+                                   (c.conv <= 1 || c.conv_w),
+                               "engine: layer %d branch %d: bad norm, chunk or convolution options", l, k);
+                    if (c.kv_lender > 0) {
+                        // the keys and values of an earlier layer: same key heads and sizes, no cache of its own
+                        FT_REQUIRE(c.kv_lender - 1 < l && c.v_role == 0, "engine: layer %d reads the keys of layer %d, which does not precede it", l,
+                                   c.kv_lender - 1);
+                        const ft_layer_desc& src = L.layers[c.kv_lender - 1].d;
+                        int found = -1;
+                        for (int j = 0; j < (src.mixer == FT_MIXER_BRANCHES ? src.n_branches : 0) && found < 0; ++j)
+                            if (src.branch[j].kind == FT_BRANCH_WINDOW_ATTENTION && src.branch[j].kv_lender == 0) found = j;
+                        FT_REQUIRE(found >= 0 && src.branch[found].kv_heads == c.kv_heads && src.branch[found].dim == c.dim &&
+                                       src.branch[found].vdim == c.vdim && src.branch[found].o_v >= 0,
+                                   "engine: layer %d: layer %d has no keys and values of its sizes to lend", l, c.kv_lender - 1);
+                        ll.lender_branch[k] = found;
+                    } else {
+                        ll.br_cache_off[k] = kv_floats;
+                        kv_floats += (size_t)e->cfg.num_pages * kKvTile * c.kv_heads * (c.dim + c.vdim);
+                    }
+                    if (c.conv >= 1) {           // the last conv - 1 projected q | k | v rows of the sequence
+                        const size_t ch = (size_t)c.heads * c.dim + (c.kv_lender > 0 ? 0 : (size_t)c.kv_heads * (c.dim + c.vdim));
+                        FT_REQUIRE(c.kv_lender > 0 ? true : (c.o_k == c.o_q + c.heads * c.dim && c.o_v == c.o_k + c.kv_heads * c.dim),
+                                   "engine: layer %d branch %d: convolved q, k, v are adjacent columns", l, k);
+                        ll.br_x_off[k] = L.slot_stride;
+                        L.slot_stride += ch * (size_t)(c.conv - 1);
+                        br_v = std::max(br_v, ch);
+                        if (c.conv > 1) L.n_stateful++;
+                    }
                     br_q = std::max(br_q, (size_t)c.heads * c.dim);
                     if (c.v_role) {
                         FT_REQUIRE(vfirst_cols == 0 || vfirst_cols == (size_t)c.kv_heads * c.vdim,
@@ -1625,6 +1760,17 @@ static int engine_init_layered(Engine* e) {
                     L.slot_stride += ch * (size_t)std::max(c.conv - 1, 0);
                     br_v = std::max(br_v, ch);
                     br_o = std::max(br_o, hv);
+                    L.n_stateful++;
+                } else if (c.kind == FT_BRANCH_SELECTIVE_SCAN) {
+                    FT_REQUIRE(c.vdim == 1 && c.conv >= 1 && c.conv <= 16 && c.conv_w && c.dt_bias && c.a_log && c.skip && c.dt_rank >= 1 &&
+                                   c.w_x && c.w_dt && c.o_v >= 0 && c.o_z >= 0 && c.dim <= 256,
+                               "engine: selective-scan layer %d branch %d is incomplete", l, k);
+                    ll.br_s_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads * c.dim;
+                    ll.br_x_off[k] = L.slot_stride;
+                    L.slot_stride += (size_t)c.heads * (size_t)(c.conv - 1);
+                    br_v = std::max(br_v, (size_t)c.heads);
+                    buf = std::max(buf, std::max((size_t)c.heads, (size_t)c.dt_rank + 2 * c.dim));
                     L.n_stateful++;
                 } else {
                     FT_REQUIRE(false, "engine: layer %d branch %d has an unknown kind %d", l, k, c.kind);
@@ -1701,6 +1847,7 @@ static int engine_init_layered(Engine* e) {
     if (vfirst_cols) FT_TRY(alloc(&L.v_first, T * vfirst_cols * 4));
     if (lstage_cols) FT_TRY(alloc(&L.lstage, T * lstage_cols * 4));
     if (L.postnorm) FT_TRY(alloc(&L.resid2, T * W * 4));
+    if (L.hyper) FT_TRY(alloc(&L.streams, T * (size_t)std::max(M.streams, 1) * W * 4));
     FT_TRY(alloc(&L.ffa, T * act_cols * 2 * 4));
     FT_TRY(alloc(&L.ffb, T * act_cols * 4));
     FT_TRY(alloc(&L.rlog, T * e_max_s * 4));
@@ -1772,7 +1919,7 @@ static void engine_free(Engine* e) {
         cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.kv_cache); cudaFree(L.bq); cudaFree(L.bv); cudaFree(L.bo); cudaFree(L.bfin); cudaFree(L.ab); cudaFree(L.gates);
-        cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage); cudaFree(L.resid2);
+        cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage); cudaFree(L.resid2); cudaFree(L.streams);
         cudaFree(L.floor); cudaFree(L.mix2); cudaFree(L.ffa); cudaFree(L.ffb); cudaFree(L.rlog);
         cudaFree(L.wts); cudaFree(L.xlast); cudaFree(L.ids); cudaFree(L.seg); cudaFree(L.slot_token);
         cudaFree(L.slot_pos); cudaFree(L.trail); cudaFree(L.pl_hi); cudaFree(L.pl_lo); cudaFree(L.hn_hi); cudaFree(L.hn_lo);

@@ -215,6 +215,13 @@ struct WindowArgs {
     float* v_first = nullptr;                     // [T][G * vdim] of the step
     int v_in_key = -1;                            // >= 0: the value of a key head is columns v_in_key .. + vdim of its (rotated) key;
                                                   // the cache row then holds the keys only
+    // qk_norm 2: one root mean square over all query heads and one over all key heads.  q_gain / k_gain: gains on the normed
+    // vectors, [dim] shared by the heads (qk_norm 1) or [H * dim] / [G * dim] (qk_norm 2)
+    const float *q_gain = nullptr, *k_gain = nullptr;
+    int rot_half = 0;                             // rotated pairs (i, i + rot_dims / 2) instead of (2i, 2i + 1)
+    float rot_mag = 1.f;                          // factor on cos and sin
+    int chunked = 0;                              // position p sees the keys from (p / window) * window on, not the last `window`
+    int no_kv = 0;                                // the cache belongs to another layer, which has written the step's rows: queries only
 };
 // The step's prompt portions as the batch builder lists them: 64-token query tiles (request, first token), and per request
 // its first row in the step, its page-table row and the position of its first token.
@@ -263,7 +270,8 @@ struct SpaceArgs {                                // state space: convolution + 
     int ldp = 0, o_x = 0, o_dt = 0, channels = 0, taps = 0, heads = 0;
     const float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr;
     float* xbc = nullptr;                         // out [T][channels]
-    float* ab = nullptr;                          // out [T][heads][2]
+    int act = 1;                                  // 1: SiLU on the convolution's result; 0: the result as it is
+    float* ab = nullptr;                          // out [T][heads][2] (heads == 0: no step sizes or decays are formed)
     float* state = nullptr;
     long long slot_stride = 0, tail_off = 0;      // tails [channels][taps - 1] of this layer inside a slot
     const int *seq_rows = nullptr, *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
@@ -342,6 +350,54 @@ int launch_rms_cols(const float* src, int lds, int src_off, const float* w, floa
 // (rank latent columns, then rot columns, at o_k; latent gain w)
 int launch_latent_stage(const float* q, int heads, int dim, int rot, const float* proj, int ldp, int o_k, int rank, const float* w,
                         float eps, float* stage, int lds, int T, cudaStream_t stream);
+
+// ---- hyper.cu (FT_LAYER_HYPER: streams joined by small matrices, layer norms; selective scan; experts that read scaled rows)
+// One kernel per sublayer joint, one CTA per row.  With `tokens`: X_s = embed[token] * scale for every stream (a step's
+// first joint).  Otherwise y = s0 * f0(y0) + s1 * f1(y1) + sum_k wt[t, k] * eout[slot_pos[t, k]] (every part optional;
+// f_i = y_i / rms(y_i) * g_i when g_i is given, wt null = ones) and X_t <- sum_s mix[s][t] X_s + out[t] * y.  Then what reads
+// the streams next: u = sum_s in_next[s] X_s (null: the plain sum), hn = (u - mean) / sqrt(var + eps) * nw + nb (+ planes).
+struct HyperArgs {
+    float* X = nullptr;                           // [T][S][W]
+    int S = 1, W = 0;
+    float eps = 0.f;
+    const int* tokens = nullptr;
+    const void* embed = nullptr;                  // bf16 [vocab][W]
+    float embed_scale = 1.f;
+    const float *y0 = nullptr, *y1 = nullptr, *g0 = nullptr, *g1 = nullptr;
+    float s0 = 1.f, s1 = 1.f;
+    const float *eout = nullptr, *wt = nullptr;
+    const int* slot_pos = nullptr;
+    int top = 0;
+    const float *mix = nullptr, *out = nullptr;   // [S][S] (from, to), [S]; null: identity, ones
+    const float* in_next = nullptr;               // [S]
+    const float *nw = nullptr, *nb = nullptr;     // gain and bias of the norm that follows
+    float* hn = nullptr;
+    void *hi = nullptr, *lo = nullptr;
+    float* sum_out = nullptr;                     // [T][W] or null: the plain sum of the new streams
+};
+int launch_hyper_joint(const HyperArgs& a, int T, cudaStream_t stream);
+// dst[slot_pos[i]] = wt[i] * src[i / top] for the T * top (token, choice) pairs: the rows the experts read when a score scales
+// its expert's input.  dst fp32 [pairs][W] and / or bf16 planes hi, lo.
+int launch_scaled_rows(const float* src, const float* wt, const int* slot_pos, int top, float* dst, void* hi, void* lo, int pairs,
+                       int W, cudaStream_t stream);
+// Selective scan: per (request, channel c) over the request's rows in order
+//   dt = softplus(dt_raw[t][c] + dt_bias[c]);  S[n] <- exp(-exp(a_log[c][n]) dt) S[n] + dt x[t][c] B[t][n]
+//   out[t][c] = (sum_n S[n] C[t][n] + skip[c] x[t][c]) * silu(z[t][c])
+// S [channels][N] of a slot at s_off, zero at a sequence's start.
+struct ScanArgs {
+    const float* x = nullptr;                     // [T][ldx] convolved inputs
+    const float* dt_raw = nullptr;                // [T][ldd]
+    const float *B = nullptr, *C = nullptr;       // rows of stride ldbc, N numbers each
+    const float* z = nullptr;                     // rows of stride ldz
+    int ldx = 0, ldd = 0, ldbc = 0, ldz = 0;
+    const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr;
+    float* out = nullptr;                         // [T][channels]
+    float* state = nullptr;
+    long long slot_stride = 0, s_off = 0;
+    const int *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
+    int channels = 0, N = 0;
+};
+int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream);
 
 // ---- sampling.cu
 int launch_sample(const float* logits, int B, int V, const float* temperature, const int* top_k,

@@ -1,0 +1,246 @@
+// Kernels of the hyper-connected layer form (FT_LAYER_HYPER) and of what its mixers and feed-forward add to the family.
+// Everything here is fp32: the streams, their small mixing matrices, norms, step sizes, decays and the recurrent state.
+//
+//   joint            the ONE kernel between two GEMM chains of a layer, one CTA per row: the sublayer's result (up to two branch
+//                    outputs, each optionally divided by its root mean square over the width and multiplied by a gain; or the
+//                    experts' rows) joins all streams at once, X_t <- sum_s mix[s][t] X_s + out[t] y; then the row that the next
+//                    sublayer (or the head) reads, u = sum_s in[s] X_s, passes its layer norm and is written with its bf16
+//                    planes.  A step's first joint fills the streams from the embedding table instead
+//   scaled rows      the rows a mixture of experts reads when a chosen score multiplies the expert's input
+//   selective scan   S[c][n] <- exp(A[c][n] dt_c) S[c][n] + dt_c x_c B_n,  y_c = S[c] . C + D_c x_c, gated by silu(z): a few
+//                    lanes share a channel and hold its states in registers; a request's tokens in order
+#include "common.cuh"
+#include "ft_internal.h"
+
+#include <algorithm>
+
+namespace ft {
+namespace {
+
+__device__ __forceinline__ float silu_h(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_h(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+__device__ __forceinline__ float cta_total(float v, float* red) {      // red: >= 33 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+constexpr int kMaxStreams = 16;
+
+// MS: streams a thread keeps in registers (the arrays are indexed by unrolled loops)
+template <int MS>
+__global__ void __launch_bounds__(256) hyper_joint_kernel(HyperArgs a) {
+    __shared__ float red[33];
+    __shared__ float smix[kMaxStreams * kMaxStreams], sout[kMaxStreams], sin_[kMaxStreams];
+    extern __shared__ float row[];               // [W]: the row the next norm reads
+    const int t = blockIdx.x, W = a.W, S = a.S;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) smix[i] = a.mix ? a.mix[i] : (i / S == i % S ? 1.f : 0.f);
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        sout[i] = a.out ? a.out[i] : 1.f;
+        sin_[i] = a.in_next ? a.in_next[i] : 1.f;
+    }
+    float r0 = 1.f, r1 = 1.f;
+    if (a.g0 || a.g1) {                          // branch results that are normed over the width before they are summed
+        float q0 = 0.f, q1 = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            if (a.g0) { const float v = a.y0[(size_t)t * W + c]; q0 = fmaf(v, v, q0); }
+            if (a.g1) { const float v = a.y1[(size_t)t * W + c]; q1 = fmaf(v, v, q1); }
+        }
+        if (a.g0) r0 = 1.f / sqrtf(cta_total(q0, red) / (float)W + a.eps);
+        if (a.g1) r1 = 1.f / sqrtf(cta_total(q1, red) / (float)W + a.eps);
+    }
+    __syncthreads();
+    float* X = a.X + (size_t)t * S * W;
+    float total = 0.f;
+    if (a.tokens) {
+        const __nv_bfloat16* er = (const __nv_bfloat16*)a.embed + (size_t)a.tokens[t] * W;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float x = __bfloat162float(er[c]) * a.embed_scale;
+            for (int s = 0; s < S; ++s) X[(size_t)s * W + c] = x;
+            float u = 0.f;
+            for (int s = 0; s < S; ++s) u = fmaf(sin_[s], x, u);
+            row[c] = u;
+            total += u;
+            if (a.sum_out) a.sum_out[(size_t)t * W + c] = x * (float)S;
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            float y = 0.f;
+            if (a.y0) y = a.s0 * (a.g0 ? a.y0[(size_t)t * W + c] * r0 * a.g0[c] : a.y0[(size_t)t * W + c]);
+            if (a.y1) y = fmaf(a.s1, a.g1 ? a.y1[(size_t)t * W + c] * r1 * a.g1[c] : a.y1[(size_t)t * W + c], y);
+            for (int k = 0; k < a.top; ++k) {
+                const float e = a.eout[(size_t)a.slot_pos[(size_t)t * a.top + k] * W + c];
+                y = a.wt ? fmaf(a.wt[(size_t)t * a.top + k], e, y) : y + e;
+            }
+            float xs[MS];
+#pragma unroll
+            for (int s = 0; s < MS; ++s) xs[s] = s < S ? X[(size_t)s * W + c] : 0.f;
+            float u = 0.f, sum = 0.f;
+#pragma unroll
+            for (int to = 0; to < MS; ++to) {
+                if (to < S) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int s = 0; s < MS; ++s)
+                        if (s < S) v = fmaf(smix[s * S + to], xs[s], v);
+                    v = fmaf(sout[to], y, v);
+                    X[(size_t)to * W + c] = v;
+                    u = fmaf(sin_[to], v, u);
+                    sum += v;
+                }
+            }
+            row[c] = u;
+            total += u;
+            if (a.sum_out) a.sum_out[(size_t)t * W + c] = sum;
+        }
+    }
+    if (!a.hn) return;
+    const float mean = cta_total(total, red) / (float)W;
+    float dev = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float d = row[c] - mean;
+        dev = fmaf(d, d, dev);
+    }
+    const float rstd = 1.f / sqrtf(cta_total(dev, red) / (float)W + a.eps);
+    __nv_bfloat16 *hi = (__nv_bfloat16*)a.hi, *lo = (__nv_bfloat16*)a.lo;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = (row[c] - mean) * rstd * a.nw[c] + (a.nb ? a.nb[c] : 0.f);
+        a.hn[(size_t)t * W + c] = v;
+        if (hi) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            hi[(size_t)t * W + c] = h;
+            lo[(size_t)t * W + c] = __float2bfloat16_rn(v - __bfloat162float(h));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) scaled_rows_kernel(const float* __restrict__ src, const float* __restrict__ wt,
+                                                          const int* __restrict__ slot_pos, int top, float* __restrict__ dst,
+                                                          __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo, int W) {
+    const int i = blockIdx.x;
+    const float w = wt[i];
+    const float* s = src + (size_t)(i / top) * W;
+    const size_t o = (size_t)slot_pos[i] * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = w * s[c];
+        if (dst) dst[o + c] = v;
+        if (hi) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            hi[o + c] = h;
+            lo[o + c] = __float2bfloat16_rn(v - __bfloat162float(h));
+        }
+    }
+}
+
+// LPC lanes (a power of two, neighbours in a warp) share a channel; lane s of them holds states s, s + LPC, s + 2 LPC, ...
+// (at most kScanKeep each).  What a token brings — dt, x, z, B, C — does not depend on the state, so the loads of the next
+// token are issued before the arithmetic of this one.
+constexpr int kScanThreads = 128, kScanKeep = 8;
+__global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(ScanArgs a, int lpc) {
+    const int r = blockIdx.y;
+    const int start = a.req_start[r], n_tok = a.req_start[r + 1] - start;
+    if (n_tok <= 0) return;
+    const int per = kScanThreads / lpc;
+    const int c = blockIdx.x * per + threadIdx.x / lpc, s = threadIdx.x % lpc;
+    const bool live = c < a.channels;
+    const int cc = live ? c : a.channels - 1;
+    float* Sg = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)cc * a.N;
+    const bool fresh = a.req_pos0[r] == 0;
+    float S[kScanKeep], A[kScanKeep];
+#pragma unroll
+    for (int i = 0; i < kScanKeep; ++i) {
+        const int n = s + lpc * i;
+        const bool ok = n < a.N;
+        S[i] = ok && !fresh ? Sg[n] : 0.f;
+        A[i] = ok ? -expf(a.a_log[(size_t)cc * a.N + n]) : 0.f;
+    }
+    const float bias = a.dt_bias[cc], skip = a.skip[cc];
+    float dtr, x, z, Bn[kScanKeep], Cn[kScanKeep];
+    auto fetch = [&](int t) {
+        dtr = a.dt_raw[(size_t)t * a.ldd + cc];
+        x = a.x[(size_t)t * a.ldx + cc];
+        z = a.z[(size_t)t * a.ldz + cc];
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) {
+            const int n = s + lpc * i;
+            Bn[i] = n < a.N ? a.B[(size_t)t * a.ldbc + n] : 0.f;
+            Cn[i] = n < a.N ? a.C[(size_t)t * a.ldbc + n] : 0.f;
+        }
+    };
+    fetch(start);
+    for (int k = 0; k < n_tok; ++k) {
+        const int t = start + k;
+        const float dt = softplus_h(dtr + bias), x0 = x, z0 = z, dx = dt * x;
+        float b0[kScanKeep], c0[kScanKeep];
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) { b0[i] = Bn[i]; c0[i] = Cn[i]; }
+        if (k + 1 < n_tok) fetch(t + 1);
+        float y = 0.f;
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) {
+            S[i] = fmaf(expf(dt * A[i]), S[i], dx * b0[i]);
+            y = fmaf(S[i], c0[i], y);
+        }
+        for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+        if (live && s == 0) a.out[(size_t)t * a.channels + c] = fmaf(skip, x0, y) * silu_h(z0);
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) {
+            const int n = s + lpc * i;
+            if (n < a.N) Sg[n] = S[i];
+        }
+    }
+}
+
+}  // namespace
+
+int launch_hyper_joint(const HyperArgs& a, int T, cudaStream_t stream) {
+    FT_REQUIRE(a.X && a.S >= 1 && a.S <= kMaxStreams && a.W >= 1, "hyper joint: 1 to %d streams (got %d)", kMaxStreams, a.S);
+    FT_REQUIRE(a.tokens ? a.embed != nullptr : (a.y0 || a.y1 || a.top > 0), "hyper joint: nothing to join");
+    FT_REQUIRE((!a.g0 || a.y0) && (!a.g1 || a.y1) && (a.top == 0 || (a.eout && a.slot_pos)) && (!a.hn || a.nw),
+               "hyper joint: missing operands");
+    const size_t smem = (size_t)a.W * 4;
+    if (a.S <= 4) hyper_joint_kernel<4><<<T, 256, smem, stream>>>(a);
+    else if (a.S <= 8) hyper_joint_kernel<8><<<T, 256, smem, stream>>>(a);
+    else hyper_joint_kernel<kMaxStreams><<<T, 256, smem, stream>>>(a);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_scaled_rows(const float* src, const float* wt, const int* slot_pos, int top, float* dst, void* hi, void* lo, int pairs,
+                       int W, cudaStream_t stream) {
+    FT_REQUIRE(src && wt && slot_pos && top >= 1 && (dst || (hi && lo)), "scaled rows: missing operands");
+    if (pairs <= 0) return 0;
+    scaled_rows_kernel<<<pairs, 256, 0, stream>>>(src, wt, slot_pos, top, dst, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, W);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream) {
+    FT_REQUIRE(a.channels >= 1 && a.N >= 1 && a.N <= 32 * kScanKeep, "selective scan: 1 to %d states per channel (got %d)",
+               32 * kScanKeep, a.N);
+    FT_REQUIRE(a.x && a.dt_raw && a.B && a.C && a.z && a.dt_bias && a.a_log && a.skip && a.out && a.state, "selective scan: missing operands");
+    // lanes per channel: about four states per lane; more lanes when the grid would leave SMs idle
+    int lpc = 1;
+    while (lpc < 32 && lpc * 4 < a.N) lpc <<= 1;
+    while (lpc < 32 && (long long)n_req * ((a.channels * lpc + kScanThreads - 1) / kScanThreads) < 148 && lpc < a.N) lpc <<= 1;
+    while (lpc * kScanKeep < a.N) lpc <<= 1;
+    const int per = kScanThreads / lpc;
+    dim3 grid((a.channels + per - 1) / per, n_req);
+    selective_scan_kernel<<<grid, kScanThreads, 0, stream>>>(a, lpc);
+    FT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace ft

@@ -19,6 +19,14 @@ query latent, a shared rotated key part and a window (one shared key head in the
 delta rule with one decay per head and token and a SiLU gate (the channel-delta kernels with the decay written to all of a
 head's channels) — and a dense SwiGLU feed-forward.
 
+The fourth design is Lotinex: pre-norm layers (layer norms with gain and bias) over several copies of the stream that small
+per-sublayer matrices mix ("hyper-connections"), three mixers — grouped-query attention inside fixed runs of positions, with
+per-head RMS-normed queries and keys, half-split rotary pairs and, optionally, the keys and values of an earlier layer; the
+gated delta rule with one decay per head; and a "parallel" mixer that averages a sliding-window attention (short
+convolutions on q, k, v, one RMS norm over all heads, stretched rotary frequencies, capped scores, a zero-score sink) with a
+selective state-space scan, each side RMS-normed over the width — and a feed-forward that is a dense SwiGLU or a mixture of
+experts whose sigmoid scores multiply the experts' inputs.  Its logits come from the embedding table itself.
+
 The reference names models by tag only and owns no model code (app/utils/config.py:86, docker-compose.vllm.yml:39); this
 module is the model side of what its engine container would load: config.json -> LayeredSpec, model.safetensors -> the
 tensors by their names in the file, pack() -> the device arrays and descriptors the native engine reads.
@@ -35,16 +43,19 @@ import torch
 
 MIXER_LATENT_ATTENTION, MIXER_CHANNEL_DELTA, MIXER_BRANCHES = 1, 2, 3
 FF_NONE, FF_MOE, FF_DENSE = 0, 1, 2
-LAYER_GATED, LAYER_SANDWICH, LAYER_POSTNORM = 0, 1, 2
+LAYER_GATED, LAYER_SANDWICH, LAYER_POSTNORM, LAYER_HYPER = 0, 1, 2, 3
 ACT_SWIGLU, ACT_RELU2 = 0, 1
 ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 BRANCH_WINDOW_ATTENTION, BRANCH_DECAY_ATTENTION, BRANCH_MATRIX_MEMORY, BRANCH_STATE_SPACE, BRANCH_LATENT_WINDOW = 1, 2, 3, 4, 5
+BRANCH_SELECTIVE_SCAN = 6
 MIXERS = {"latent_attention": MIXER_LATENT_ATTENTION, "channel_delta": MIXER_CHANNEL_DELTA,
           "mlstm": MIXER_BRANCHES, "mamba2": MIXER_BRANCHES, "parallel": MIXER_BRANCHES}
 BRANCHES = {"window_attention": BRANCH_WINDOW_ATTENTION, "decay_attention": BRANCH_DECAY_ATTENTION,
-            "matrix_memory": BRANCH_MATRIX_MEMORY, "state_space": BRANCH_STATE_SPACE, "latent_window": BRANCH_LATENT_WINDOW}
+            "matrix_memory": BRANCH_MATRIX_MEMORY, "state_space": BRANCH_STATE_SPACE, "latent_window": BRANCH_LATENT_WINDOW,
+            "selective_scan": BRANCH_SELECTIVE_SCAN}
 POSTNORM_MIXERS = ("attention", "latent_attention", "delta")      # Vonedra's names for its mixers
 SANDWICH_MIXERS = ("mlstm", "mamba2", "parallel")
+HYPER_MIXERS = ("attention", "delta", "parallel")                 # Lotinex's names for its mixers
 
 
 @dataclass(frozen=True)
@@ -77,6 +88,15 @@ class BranchSpec:
     # latent window attention: dim = plain query/key size per head, rot_dims = rotated size
     kv_rank: int = 0
     q_rank: int = 0
+    # window attention options (Lotinex's attention and the left side of its parallel mixer); conv above = taps on q, k, v
+    qk_gain: str = ""               # "" | "head" (gain [dim] shared by the heads) | "all" (one norm and gains over all heads)
+    rot_half: bool = False          # rotated pairs (i, i + rot_dims / 2)
+    rot_scaling: Tuple[float, ...] = ()      # (factor, original, fast, slow): slow pairs slowed by factor, cos / sin magnified
+    chunked: bool = False           # runs of `window` positions instead of a sliding window
+    zero_sink: bool = False         # one more term exp(0) in the softmax denominator
+    kv_from: int = -1               # layer whose keys and values this one reads
+    out_norm_width: bool = False    # the projected output is RMS-normed over the width (gain '<side>out')
+    dt_rank: int = 0                # selective scan (heads = channels, dim = states per channel)
 
 
 @dataclass(frozen=True)
@@ -97,7 +117,7 @@ class LayerSpec:
     groups: int = 1
     keep: int = 1
     # sandwich layers (Gedelorn)
-    form: str = "gated"             # "gated" | "sandwich" | "postnorm"
+    form: str = "gated"             # "gated" | "sandwich" | "postnorm" | "hyper"
     branches: Tuple[BranchSpec, ...] = ()
     ff_kind: str = ""               # sandwich: "" (none) | "dense" | "moe"
     route_scale: float = 1.0
@@ -113,8 +133,9 @@ class LayeredSpec:
     eps: float
     logit_softcap: float
     layers: Tuple[LayerSpec, ...] = field(default_factory=tuple)
-    embed_scale: float = 1.0        # post-norm models
+    embed_scale: float = 1.0        # post-norm and hyper-connected models
     canon_taps: int = 0             # post-norm models: taps of the input convolutions
+    streams: int = 0                # hyper-connected models: copies of the stream (0: one, and no mixing tensors)
 
     # the attributes the serving code reads from any model spec
     @property
@@ -124,6 +145,13 @@ class LayeredSpec:
     def config(self) -> Dict:
         """The config.json of this spec."""
         out = []
+        if self.layers and self.layers[0].form == "hyper":
+            cfg = {"architecture": self.architecture, "embedding": {"scale": self.embed_scale},
+                   "layers": [_hyper_layer_config(l) for l in self.layers], "norm": {"eps": self.eps}, "vocab": self.vocab,
+                   "width": self.width}
+            if self.streams:
+                cfg["streams"] = self.streams
+            return cfg
         for l in self.layers:
             if l.form == "sandwich":
                 out.append(_sandwich_layer_config(l))
@@ -148,6 +176,94 @@ class LayeredSpec:
             cfg["canon"] = {"taps": self.canon_taps}
             cfg["embedding"] = {"scale": self.embed_scale}
         return cfg
+
+
+def _hyper_attention_config(b: BranchSpec) -> Dict:
+    m = {"dim": b.dim, "heads": b.heads, "kv_heads": b.kv_heads, "scale": b.scale, "vdim": b.vdim}
+    if b.window:
+        m["mask"] = {"size": b.window}
+    if b.rot_dims:
+        m["rot"] = {"base": b.rot_base, "dims": b.rot_dims}
+        if b.rot_scaling:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), b.rot_scaling))
+    if b.softcap:
+        m["softcap"] = b.softcap
+    if b.conv:
+        m["conv"] = b.conv
+    if b.kv_from >= 0:
+        m["kv_from"] = b.kv_from
+    return m
+
+
+def _hyper_layer_config(l: LayerSpec) -> Dict:
+    if l.mixer == "delta":
+        mixer = {"conv": l.conv, "dim": l.dim, "heads": l.heads, "kv_heads": l.kv_heads, "vdim": l.vdim}
+    elif l.mixer == "attention":
+        mixer = _hyper_attention_config(l.branches[0])
+    else:
+        left, right = l.branches
+        mixer = {"left": _hyper_attention_config(left),
+                 "right": {"conv": right.conv, "dt_rank": right.dt_rank, "inner": right.heads, "state": right.dim}}
+    mlp = None
+    if l.ff_kind == "dense":
+        mlp = {"ff": l.ff, "kind": "dense"}
+    elif l.ff_kind == "moe":
+        mlp = {"expert": {"ff": l.ff}, "kind": "moe", "router": {"experts": l.experts, "top": l.top}}
+    return {"mixer": mixer, "mlp": mlp, "type": l.mixer}
+
+
+def _hyper_attention_from_config(m: Dict, **kw) -> BranchSpec:
+    rot = m.get("rot") or {}
+    sc = rot.get("scaling") or {}
+    return BranchSpec(
+        kind="window_attention", heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+        vdim=int(m.get("vdim", m["dim"])), scale=float(m["scale"]), softcap=float(m.get("softcap") or 0.0),
+        window=int((m.get("mask") or {}).get("size", 0)), rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)),
+        rot_half=True, rot_scaling=tuple(float(sc[k]) for k in ("factor", "original", "fast", "slow")) if sc else (),
+        qk_norm=True, conv=int(m.get("conv") or 0), kv_from=int(m["kv_from"]) if m.get("kv_from") is not None else -1, **kw)
+
+
+def _hyper_layer_from_config(i: int, l: Dict) -> LayerSpec:
+    kind, m = l["type"], l["mixer"]
+    kw = dict(mixer=kind, form="hyper")
+    if kind == "attention":
+        kw["branches"] = (_hyper_attention_from_config(m, qk_gain="head", chunked=bool((m.get("mask") or {}).get("size"))),)
+    elif kind == "delta":
+        kw.update(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                  conv=int(m["conv"]))
+    elif kind == "parallel":
+        r = m["right"]
+        kw["branches"] = (
+            _hyper_attention_from_config(m["left"], prefix="left.", qk_gain="all", zero_sink=True, out_norm_width=True, out_scale=0.5),
+            BranchSpec(kind="selective_scan", heads=int(r["inner"]), kv_heads=1, dim=int(r["state"]), vdim=1, prefix="right.",
+                       conv=int(r["conv"]), dt_rank=int(r["dt_rank"]), out_norm_width=True, out_scale=0.5))
+    else:
+        raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+    mlp = l.get("mlp")
+    if mlp:
+        if mlp.get("kind") == "dense":
+            kw.update(ff_kind="dense", ff=int(mlp["ff"]))
+        elif mlp.get("kind") == "moe":
+            kw.update(ff_kind="moe", ff=int(mlp["expert"]["ff"]), experts=int(mlp["router"]["experts"]), top=int(mlp["router"]["top"]))
+        else:
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+    return LayerSpec(**kw)
+
+
+def rotary_frequencies(b: BranchSpec) -> Tuple[List[float], float]:
+    """Angle per position of every rotated pair and the factor on cos and sin.  With rot_scaling = (factor, original, fast,
+    slow): pair i turns `original * f_i / 2 pi` times over the original context; pairs that turn more than `fast` times keep
+    f_i, pairs that turn fewer than `slow` times get f_i / factor, with a linear ramp over the pair index between."""
+    import math
+    half = b.rot_dims // 2
+    f = [b.rot_base ** (-2.0 * i / b.rot_dims) for i in range(half)]
+    if not b.rot_scaling:
+        return f, 1.0
+    factor, orig, fast, slow = b.rot_scaling
+    at = lambda turns: b.rot_dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(b.rot_base))
+    lo, hi = max(math.floor(at(fast)), 0), min(math.ceil(at(slow)), b.rot_dims - 1)
+    ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(half)]
+    return [f[i] / factor * ramp[i] + f[i] * (1.0 - ramp[i]) for i in range(half)], 0.1 * math.log(factor) + 1.0
 
 
 def _postnorm_layer_config(l: LayerSpec) -> Dict:
@@ -296,8 +412,12 @@ def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = N
     """config.json (+ tensor shapes, for the sizes only a shape gives) -> LayeredSpec."""
     layers = []
     postnorm = cfg.get("architecture") == "Vonedra"
+    hyper = cfg.get("architecture") == "Lotinex"
     for i, l in enumerate(cfg["layers"]):
         kind, m = l["type"], l["mixer"]
+        if hyper:
+            layers.append(_hyper_layer_from_config(i, l))
+            continue
         if postnorm:
             layers.append(_postnorm_layer_from_config(i, l, shapes))
             continue
@@ -328,13 +448,18 @@ def spec_from_config(cfg: Dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = N
     return LayeredSpec(name=name, architecture=str(cfg.get("architecture", "Gitozen")), width=int(cfg["width"]),
                        vocab=int(cfg["vocab"]), eps=float(cfg["norm"]["eps"]), logit_softcap=float(cap) if cap else 0.0,
                        layers=tuple(layers), embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
-                       canon_taps=int((cfg.get("canon") or {}).get("taps", 0)))
+                       canon_taps=int((cfg.get("canon") or {}).get("taps", 0)), streams=int(cfg.get("streams") or 0) if hyper else 0)
 
 
 def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
     """Names and shapes of a checkpoint of this spec."""
     W = spec.width
     out: Dict[str, Tuple[int, ...]] = {"embed": (spec.vocab, W)}
+    if spec.layers and spec.layers[0].form == "hyper":
+        for i, l in enumerate(spec.layers):
+            out.update(_hyper_shapes(f"l{i}.", l, W, spec.streams))
+        out.update({"final.norm": (W,), "final.norm.b": (W,)})      # no head: the logits come from the embedding table
+        return out
     for i, l in enumerate(spec.layers):
         p = f"l{i}."
         if l.form == "sandwich":
@@ -364,6 +489,48 @@ def tensor_shapes(spec: LayeredSpec) -> Dict[str, Tuple[int, ...]]:
         out.update({p + "rg1": (W, W), p + "rg1.b": (W,)})
     out["final.norm"] = (W,) if spec.layers and spec.layers[-1].form in ("sandwich", "postnorm") else ()
     out["head"] = (spec.vocab, W)
+    return out
+
+
+def _hyper_shapes(p: str, l: LayerSpec, W: int, streams: int) -> Dict[str, Tuple[int, ...]]:
+    out: Dict[str, Tuple[int, ...]] = {p + "norm1": (W,), p + "norm1.b": (W,)}
+    m = p + "mix."
+    if l.mixer == "delta":
+        qk, hv = l.kv_heads * l.dim, l.heads * l.vdim
+        out.update({m + "q": (qk, W), m + "q.conv": (qk, l.conv), m + "k": (qk, W), m + "k.conv": (qk, l.conv),
+                    m + "v": (hv, W), m + "v.conv": (hv, l.conv), m + "b": (l.heads, W), m + "A_log": (l.heads,),
+                    m + "norm": (l.vdim,), m + "a": (l.heads, W), m + "dt_bias": (l.heads,), m + "g": (hv, W), m + "o": (W, hv)})
+    for b in l.branches:
+        q = m + b.prefix
+        if b.kind == "window_attention":
+            nq, nk, nv = b.heads * b.dim, b.kv_heads * b.dim, b.kv_heads * b.vdim
+            wide = b.qk_gain == "all"
+            out.update({q + "q": (nq, W), q + "q.norm": (nq if wide else b.dim,), q + "o": (W, b.heads * b.vdim)})
+            if b.kv_from < 0:
+                out.update({q + "k": (nk, W), q + "v": (nv, W), q + "k.norm": (nk if wide else b.dim,)})
+            if b.conv:
+                out[q + "q.conv"] = (nq, b.conv)
+                if b.kv_from < 0:
+                    out.update({q + "k.conv": (nk, b.conv), q + "v.conv": (nv, b.conv)})
+        else:
+            C, N, R = b.heads, b.dim, b.dt_rank
+            out.update({q + "in": (2 * C, W), q + "conv": (C, b.conv), q + "conv.b": (C,), q + "x": (R + 2 * N, C),
+                        q + "dt": (C, R), q + "dt.b": (C,), q + "A_log": (C, N), q + "D": (C,), q + "o": (W, C)})
+        if b.out_norm_width:
+            out[q + "out"] = (W,)
+    subs = ["hc1"]
+    if l.ff_kind:
+        out.update({p + "norm2": (W,), p + "norm2.b": (W,)})
+        subs.append("hc2")
+    if l.ff_kind == "dense":
+        out.update({p + "mlp.gate": (l.ff, W), p + "mlp.up": (l.ff, W), p + "mlp.down": (W, l.ff)})
+    elif l.ff_kind == "moe":
+        for e in range(l.experts):
+            out.update({f"{p}mlp.e{e}.gate": (l.ff, W), f"{p}mlp.e{e}.up": (l.ff, W), f"{p}mlp.e{e}.down": (W, l.ff)})
+        out[p + "mlp.router"] = (l.experts, W)
+    if streams:
+        for h in subs:
+            out.update({f"{p}{h}.in": (streams,), f"{p}{h}.out": (streams,), f"{p}{h}.mix": (streams, streams)})
     return out
 
 
@@ -434,9 +601,25 @@ def init_weights(spec: LayeredSpec, seed: int = 0, device: str = "cpu") -> Dict[
     w = {}
     sandwich = bool(spec.layers) and spec.layers[-1].form == "sandwich"
     postnorm = bool(spec.layers) and spec.layers[-1].form == "postnorm"
+    hyper = bool(spec.layers) and spec.layers[-1].form == "hyper"
     for name, shape in tensor_shapes(spec).items():
         leaf = name.split(".")[-1]
-        if postnorm and leaf in ("canon1", "canon2"):
+        part = name.split(".")[-2] if "." in name else ""
+        if hyper and part in ("hc1", "hc2"):
+            n = shape[0]
+            if leaf == "mix":                                    # mostly each stream to itself
+                t = torch.eye(n) * 0.8 + 0.2 / n + 0.1 * torch.randn(shape, generator=g)
+            elif leaf == "in":
+                t = 1.0 / n + 0.2 * torch.randn(shape, generator=g)
+            else:
+                t = 0.7 + 0.3 * torch.randn(shape, generator=g)
+        elif hyper and leaf == "b" and part in ("norm1", "norm2", "norm", "conv", "dt"):
+            t = 0.1 * torch.randn(shape, generator=g) - (2.0 if part == "dt" else 0.0)
+        elif hyper and (leaf in ("norm1", "norm2", "out") or (leaf == "norm" and part in ("final", "q", "k"))):
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif hyper and leaf == "D":
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif postnorm and leaf in ("canon1", "canon2"):
             t = 0.3 * torch.randn(shape, generator=g)
         elif postnorm and leaf == "dwa":
             t = 0.15 * torch.randn(shape, generator=g)
@@ -528,6 +711,9 @@ class BranchDesc(C.Structure):
         ("sink", C.c_void_p), ("rel", C.c_void_p), ("v_bias", C.c_void_p), ("o_bias", C.c_void_p), ("v_mix", C.c_void_p),
         ("kv_rank", C.c_int), ("q_rank", C.c_int),
         ("w_uq", C.c_void_p), ("w_uk_t", C.c_void_p), ("w_uv", C.c_void_p), ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p),
+        ("rot_half", C.c_int), ("chunked", C.c_int), ("kv_lender", C.c_int), ("rot_mag", C.c_float),
+        ("q_gain", C.c_void_p), ("k_gain", C.c_void_p), ("out_gain", C.c_void_p),
+        ("dt_rank", C.c_int), ("w_x", C.c_void_p), ("w_dt", C.c_void_p),
     ]
 
 
@@ -551,6 +737,8 @@ class LayerDesc(C.Structure):
         ("ff_act", C.c_int), ("route_kind", C.c_int), ("route_norm", C.c_int), ("route_scale", C.c_float),
         ("w_router", C.c_void_p), ("router_rows", C.c_int), ("shared_ff", C.c_int), ("w_shared_up", C.c_void_p), ("w_shared_down", C.c_void_p),
         ("canon_taps", C.c_int), ("canon1", C.c_void_p), ("canon2", C.c_void_p), ("depth_w", C.c_void_p), ("gate_act", C.c_int),
+        ("norm_pre1_b", C.c_void_p), ("norm_pre2_b", C.c_void_p),
+        ("hc_in", C.c_void_p * 2), ("hc_out", C.c_void_p * 2), ("hc_mix", C.c_void_p * 2), ("route_input", C.c_int),
     ]
 
 
@@ -560,7 +748,7 @@ class LayeredModel(C.Structure):
         ("width", C.c_int), ("vocab", C.c_int), ("n_layers", C.c_int),
         ("eps", C.c_float), ("logit_softcap", C.c_float), ("final_norm_gain", C.c_float),
         ("embed", C.c_void_p), ("head", C.c_void_p), ("layers", C.POINTER(LayerDesc)), ("exact_f32", C.c_int),
-        ("final_norm_w", C.c_void_p), ("embed_scale", C.c_float),
+        ("final_norm_w", C.c_void_p), ("embed_scale", C.c_float), ("final_norm_b", C.c_void_p), ("streams", C.c_int),
     ]
 
 
@@ -676,6 +864,105 @@ def _pack_sandwich_layer(l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W:
             d.w_shared_down = dev(w[p + "mlp.shared.down"]).data_ptr()
 
 
+def _pack_hyper_layer(spec: LayeredSpec, i: int, l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W: int, device, dev,
+                      keep: list) -> None:
+    """Descriptor of a hyper-connected layer: layer-norm gains and biases, the stream-mixing tensors, the mixer's projections
+    stacked into w_in (q | k | v of an attention side adjacent: their convolution addresses them as one run of channels)."""
+    f32 = torch.float32
+    m = p + "mix."
+    d.form = LAYER_HYPER
+    for f_ in ("o_q", "o_k", "o_v", "o_dkv", "o_gate", "o_beta", "o_a1", "o_g1", "o_rg1", "o_rg2", "o_router"):
+        setattr(d, f_, -1)
+    d.norm_gain = 1.0
+    vec = lambda name: dev(w[name], f32).data_ptr()
+    d.norm_pre1, d.norm_pre1_b = vec(p + "norm1"), vec(p + "norm1.b")
+    for k, h in enumerate(("hc1", "hc2")):
+        if spec.streams and (k == 0 or l.ff_kind):
+            d.hc_in[k], d.hc_out[k], d.hc_mix[k] = vec(f"{p}{h}.in"), vec(f"{p}{h}.out"), vec(f"{p}{h}.mix")
+    if l.mixer == "delta":
+        d.mixer, d.heads, d.kv_heads, d.dim, d.vdim, d.conv = MIXER_CHANNEL_DELTA, l.heads, l.kv_heads, l.dim, l.vdim, l.conv
+        d.rank_a = d.rank_g = 0
+        d.gate_act = 1
+        parts = [("q", torch.cat([w[m + "q"], w[m + "k"], w[m + "v"]], 0)), ("beta", w[m + "b"]), ("a1", w[m + "a"]), ("g1", w[m + "g"])]
+    else:
+        d.mixer, d.n_branches = MIXER_BRANCHES, len(l.branches)
+        parts = []
+        for k, b in enumerate(l.branches):
+            q = m + b.prefix
+            if b.kind == "window_attention":
+                parts.append((f"{k}q", torch.cat([w[q + "q"]] + ([w[q + "k"], w[q + "v"]] if b.kv_from < 0 else []), 0)))
+            else:
+                parts.append((f"{k}x", w[q + "in"]))
+    w_in, offs = _stack_inputs([(n, t.to(device)) for n, t in parts], W, device)
+    keep.append(w_in)
+    d.w_in, d.n_in = w_in.data_ptr(), w_in.shape[0]
+    if l.mixer == "delta":
+        for n, o in offs.items():
+            setattr(d, "o_" + n, o)
+        d.o_k = d.o_q + l.kv_heads * l.dim
+        d.o_v = d.o_k + l.kv_heads * l.dim
+        d.w_o = dev(w[m + "o"]).data_ptr()
+        d.conv_w = dev(torch.cat([w[m + "q.conv"], w[m + "k.conv"], w[m + "v.conv"]], 0), f32).data_ptr()
+        d.dt_bias, d.a_log, d.out_norm = vec(m + "dt_bias"), vec(m + "A_log"), vec(m + "norm")
+    for k, b in enumerate(l.branches):
+        q, c = m + b.prefix, d.branch[k]
+        c.kind, c.heads, c.kv_heads, c.dim, c.vdim = BRANCHES[b.kind], b.heads, b.kv_heads or b.heads, b.dim, b.vdim
+        c.out_scale = b.out_scale
+        for f_ in ("o_q", "o_k", "o_v", "o_g", "o_z", "o_dt", "o_i", "o_f"):
+            setattr(c, f_, -1)
+        c.w_o = dev(w[q + "o"]).data_ptr()
+        if b.out_norm_width:
+            c.out_gain = vec(q + "out")
+        if b.kind == "window_attention":
+            own = b.kv_from < 0
+            c.o_q = offs[f"{k}q"]
+            if own:
+                c.o_k = c.o_q + b.heads * b.dim
+                c.o_v = c.o_k + c.kv_heads * b.dim
+            else:
+                c.kv_lender = b.kv_from + 1
+            c.scale, c.softcap, c.window, c.rot_dims, c.chunked = b.scale, b.softcap, b.window, b.rot_dims, int(b.chunked)
+            c.rot_half = int(b.rot_half)
+            if b.rot_dims:
+                freq, mag = rotary_frequencies(b)
+                c.rot_freq, c.rot_mag = dev(torch.tensor(freq, dtype=torch.float64), f32).data_ptr(), mag
+            c.qk_norm = (2 if b.qk_gain == "all" else 1) if b.qk_norm else 0
+            if b.qk_gain:
+                c.q_gain = vec(q + "q.norm")
+                if own:
+                    c.k_gain = vec(q + "k.norm")
+            if b.zero_sink:
+                c.sink = dev(torch.zeros(b.heads), f32).data_ptr()
+            if b.conv:
+                c.conv = b.conv
+                c.conv_w = dev(torch.cat([w[q + n + ".conv"] for n in ("qkv" if own else "q")], 0), f32).data_ptr()
+        else:
+            C_ = b.heads
+            c.o_v = offs[f"{k}x"]
+            c.o_z = c.o_v + C_
+            c.conv, c.dt_rank = b.conv, b.dt_rank
+            c.conv_w, c.conv_b = vec(q + "conv"), vec(q + "conv.b")
+            c.w_x, c.w_dt = dev(w[q + "x"]).data_ptr(), dev(w[q + "dt"]).data_ptr()
+            c.dt_bias, c.a_log, c.skip = vec(q + "dt.b"), vec(q + "A_log"), vec(q + "D")
+    d.ff_kind = FF_NONE
+    if l.ff_kind:
+        d.norm_pre2, d.norm_pre2_b = vec(p + "norm2"), vec(p + "norm2.b")
+        d.ff, d.ff_act = l.ff, ACT_SWIGLU
+    if l.ff_kind == "dense":
+        d.ff_kind = FF_DENSE
+        d.w_gu = dev(_interleave(w[p + "mlp.gate"].to(device), w[p + "mlp.up"].to(device))).data_ptr()
+        d.w_down = dev(w[p + "mlp.down"]).data_ptr()
+    elif l.ff_kind == "moe":
+        d.ff_kind, d.experts, d.top, d.groups, d.keep = FF_MOE, l.experts, l.top, 1, 1
+        d.route_kind, d.route_norm, d.route_scale, d.route_input = ROUTE_SIGMOID, 0, 1.0, 1
+        router = torch.zeros((l.experts + 127) // 128 * 128, W, dtype=torch.bfloat16, device=device)
+        router[:l.experts] = w[p + "mlp.router"].to(device)
+        d.w_router, d.router_rows = dev(router).data_ptr(), router.shape[0]
+        gu = torch.stack([_interleave(w[f"{p}mlp.e{e}.gate"].to(device), w[f"{p}mlp.e{e}.up"].to(device)) for e in range(l.experts)])
+        d.w_gu = dev(gu).data_ptr()
+        d.w_down = dev(torch.stack([w[f"{p}mlp.e{e}.down"].to(device) for e in range(l.experts)])).data_ptr()
+
+
 def _pack_postnorm_layer(spec: LayeredSpec, i: int, l: LayerSpec, w: Dict[str, torch.Tensor], p: str, d, W: int, device, dev,
                          keep: list, first_mix: int) -> None:
     """Descriptor of a post-norm layer: gains as stored, input convolutions, depth weights, the mixer's projections stacked
@@ -778,6 +1065,9 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
         if l.form == "sandwich":
             _pack_sandwich_layer(l, w, p, d, W, device, dev, keep)
             continue
+        if l.form == "hyper":
+            _pack_hyper_layer(spec, i, l, w, p, d, W, device, dev, keep)
+            continue
         if l.form == "postnorm":
             first_mix = next((j for j, x in enumerate(spec.layers) if x.branches and x.branches[0].v_mix), -1)
             _pack_postnorm_layer(spec, i, l, w, p, d, W, device, dev, keep, first_mix)
@@ -836,14 +1126,20 @@ def pack(spec: LayeredSpec, w: Dict[str, torch.Tensor], device, exact_f32: bool 
     model.width, model.vocab, model.n_layers = W, spec.vocab, len(spec.layers)
     model.eps, model.logit_softcap = spec.eps, spec.logit_softcap
     postnorm = bool(spec.layers) and spec.layers[0].form == "postnorm"
-    if w["final.norm"].dim() == 0:
+    hyper = bool(spec.layers) and spec.layers[0].form == "hyper"
+    if hyper:                                # a layer norm with gain and bias; the logits come from the embedding table
+        model.final_norm_gain = 1.0
+        model.final_norm_w = dev(w["final.norm"], torch.float32).data_ptr()
+        model.final_norm_b = dev(w["final.norm.b"], torch.float32).data_ptr()
+        model.streams = max(spec.streams, 1)
+    elif w["final.norm"].dim() == 0:
         model.final_norm_gain = float(w["final.norm"].float().item())
     else:
         model.final_norm_gain = 1.0          # sandwich models store gain - 1, post-norm models the gain itself
         model.final_norm_w = dev(w["final.norm"].float() + (0.0 if postnorm else 1.0), torch.float32).data_ptr()
-    model.embed_scale = spec.embed_scale if postnorm else 1.0
+    model.embed_scale = spec.embed_scale if postnorm or hyper else 1.0
     model.embed = dev(w["embed"]).data_ptr()
-    model.head = dev(w["head"]).data_ptr()
+    model.head = model.embed if hyper else dev(w["head"]).data_ptr()
     model.layers = C.cast(descs, C.POINTER(LayerDesc))
     model.exact_f32 = int(exact_f32)
     keep.append(descs)

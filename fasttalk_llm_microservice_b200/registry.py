@@ -4,7 +4,7 @@ The reference picks a model by tag and leaves loading to its engine container (a
 docker-compose.vllm.yml:39); here the folder's config.json decides which loader and which engine constructor run:
 
   * Hugging Face Llama ("model_type": "llama")            -> checkpoint.load_hf_checkpoint, ModelSpec
-  * layered models ("layers": [...] + "width": Gitozen, Gedelorn, Vonedra) -> layered.load_checkpoint, LayeredSpec
+  * layered models ("layers": [...] + "width": Gitozen, Gedelorn, Vonedra, Lotinex) -> layered.load_checkpoint, LayeredSpec
 
 Engine(spec, weights, ...) accepts either kind of spec.
 """
@@ -30,7 +30,7 @@ def _layered(path, device, name):
 FAMILIES["llama"] = _llama
 FAMILIES["layered"] = _layered
 # architectures of the layered family, by the name their config.json carries
-LAYERED_ARCHITECTURES = ("Gitozen", "Gedelorn", "Vonedra")
+LAYERED_ARCHITECTURES = ("Gitozen", "Gedelorn", "Vonedra", "Lotinex")
 
 
 def family_of(cfg: Dict) -> str:

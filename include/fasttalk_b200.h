@@ -199,7 +199,13 @@ enum { FT_FF_NONE = 0, FT_FF_MOE = 1, FT_FF_DENSE = 2 };
  *                      their results are normed: x += post1(mixer(h1)); x += post2(ff(h2)).  With depth_w the stream that
  *                      goes on is a weighted sum over depth, sum_j depth_w[j] X_j, X_0 the embedding output and X_(i+1)
  *                      layer i's result before this averaging.  Takes any mixer of the family. */
-enum { FT_LAYER_GATED = 0, FT_LAYER_SANDWICH = 1, FT_LAYER_POSTNORM = 2 };
+/*   FT_LAYER_HYPER:    pre-norm layers over `streams` copies X_1 .. X_s of the stream (all equal to the embedding output at
+ *                      the start).  A sublayer reads u = sum_s hc_in[s] X_s through a layer norm with gain and bias
+ *                      ((u - mean) / sqrt(var + eps) * w + b), and every stream is rebuilt from the old ones:
+ *                      X_t <- sum_s hc_mix[s][t] X_s + hc_out[t] * sublayer(norm(u)).  The model's last norm reads the sum of
+ *                      the streams.  streams <= 1 without the hc tensors is the plain x += sublayer(norm(x)).  Takes the
+ *                      channel-delta mixer (rank_a == rank_g == 0) or branch mixers, and any feed-forward. */
+enum { FT_LAYER_GATED = 0, FT_LAYER_SANDWICH = 1, FT_LAYER_POSTNORM = 2, FT_LAYER_HYPER = 3 };
 enum { FT_ACT_SWIGLU = 0, FT_ACT_RELU2 = 1 };          /* expert: W_down (silu(W_gate h) * W_up h)  |  W_down relu(W_up h)^2 */
 enum { FT_ROUTE_SOFTMAX = 0, FT_ROUTE_SIGMOID = 1 };   /* router scores over all experts */
 
@@ -231,9 +237,25 @@ enum { FT_ROUTE_SOFTMAX = 0, FT_ROUTE_SIGMOID = 1 };   /* router scores over all
  * their true distances), sink (fp32 [heads]: exp(sink_h) joins the softmax denominator, no key, no value), rel (fp32
  * [rel_n][heads]: a bias by distance i - j, distances from rel_n - 1 on share the last row; added after scale and cap),
  * v_bias, o_bias (fp32 [width], added to the branch's projected output), v_role (1: this layer's values are kept for the
- * step as the "first" values; 2: v <- (1 - v_mix) v + v_mix v_first before they are cached). */
+ * step as the "first" values; 2: v <- (1 - v_mix) v + v_mix v_first before they are cached).
+ * More options of window attention: qk_norm 2 (ONE root mean square over all heads of q, one over all heads of k) and gains
+ * q_gain / k_gain on the normed vectors (qk_norm 1: fp32 [dim] shared by the heads; 2: fp32 [heads * dim] / [kv_heads * dim]);
+ * rot_half (the rotated pairs are (i, i + rot_dims / 2) instead of (2i, 2i + 1)); rot_mag (cos and sin are multiplied by it;
+ * 0 = 1) — stretched frequencies are the caller's business, rot_freq holds them; chunked (position i sees j <= i of its own
+ * run of `window` positions counted from 0, instead of the last `window`); conv + conv_w (q | k | v pass a short causal
+ * convolution over time right after the projection, fp32 [heads * dim + kv_heads * (dim + vdim)][conv], last column = current
+ * token, no bias; the last conv - 1 projected rows live in the session's state slot); kv_lender (n > 0: the branch has no
+ * keys and values of its own and attends over the cache of layer n - 1's first window-attention branch, which has the same
+ * key heads and sizes).
+ *   FT_BRANCH_SELECTIVE_SCAN    heads = channels, dim = N states per channel, vdim = 1.  x (columns o_v) passes a short causal
+ *                               convolution with bias and SiLU; w_x x = [dt_rank | N | N] = (low, B, C); dt = softplus(w_dt low +
+ *                               dt_bias) per channel; S[c][n] <- exp(-exp(a_log[c][n]) dt_c) S[c][n] + dt_c x_c B_n;
+ *                               y_c = sum_n S[c][n] C_n + skip[c] x_c; y *= silu(z) (columns o_z).  S and the last conv - 1
+ *                               raw x rows live in the slot.
+ * out_gain (any branch kind, fp32 [width]): the branch's projected output is divided by its root mean square over the width
+ * and multiplied by this gain before out_scale and the sum with the other branch. */
 enum { FT_BRANCH_WINDOW_ATTENTION = 1, FT_BRANCH_DECAY_ATTENTION = 2, FT_BRANCH_MATRIX_MEMORY = 3, FT_BRANCH_STATE_SPACE = 4,
-       FT_BRANCH_LATENT_WINDOW = 5 };
+       FT_BRANCH_LATENT_WINDOW = 5, FT_BRANCH_SELECTIVE_SCAN = 6 };
 typedef struct {
     int kind;                  /* FT_BRANCH_* */
     int heads, kv_heads;       /* head h reads key (value) head h / (heads / kv_heads); state space: kv_heads = groups */
@@ -274,6 +296,16 @@ typedef struct {
     const void* w_uv;          /* bf16 [heads * vdim][kv_rank] */
     const float* q_norm;       /* fp32 [q_rank] */
     const float* kv_norm;      /* fp32 [kv_rank] */
+    /* more window-attention options (see above) */
+    int rot_half, chunked, kv_lender;
+    float rot_mag;
+    const float* q_gain;
+    const float* k_gain;
+    const float* out_gain;     /* fp32 [width] */
+    /* selective scan */
+    int dt_rank;
+    const void* w_x;           /* bf16 [dt_rank + 2 * dim][heads] */
+    const void* w_dt;          /* bf16 [heads][dt_rank] */
 } ft_branch_desc;
 
 typedef struct {
@@ -334,6 +366,13 @@ typedef struct {
     /* channel delta with rank_a == 0: the decay pre-activation is one column per head of w_in at o_a1 and dt_bias is [heads]
      * (one decay per head and token); with rank_g == 0 the gate is heads * vdim columns of w_in at o_g1 */
     int gate_act;              /* channel delta: 0 = sigmoid(gate), 1 = silu(gate) */
+    /* ---- FT_LAYER_HYPER: norm_pre1 / norm_pre2 are the gains of the two layer norms, these their biases ---- */
+    const float* norm_pre1_b;  /* fp32 [width] */
+    const float* norm_pre2_b;
+    const float* hc_in[2];     /* fp32 [streams]: how sublayer q = 0 (mixer), 1 (feed-forward) reads the streams; null = ones */
+    const float* hc_out[2];    /* fp32 [streams]: how its result joins each stream; null = ones */
+    const float* hc_mix[2];    /* fp32 [streams][streams], [from][to]; null = identity */
+    int route_input;           /* mixture of experts: 1 = a chosen score multiplies its expert's INPUT (sum_e expert_e(s_e h)), not its output */
 } ft_layer_desc;
 
 typedef struct {
@@ -349,7 +388,9 @@ typedef struct {
                                   the tensor cores (tcgen05) from bf16 hi + lo planes of the fp32 activations with fp32
                                   accumulation; norms, scores, softmax, router, recurrence and residual stay fp32 */
     const float* final_norm_w; /* fp32 [width] or null: a gain per coordinate instead of final_norm_gain */
-    float embed_scale;         /* FT_LAYER_POSTNORM models: the embedding output is embed[token] * embed_scale (0 = 1) */
+    float embed_scale;         /* FT_LAYER_POSTNORM / FT_LAYER_HYPER models: the embedding output is embed[token] * embed_scale (0 = 1) */
+    const float* final_norm_b; /* FT_LAYER_HYPER models: the last norm is a layer norm with gain final_norm_w and this bias */
+    int streams;               /* FT_LAYER_HYPER models: copies of the stream (0 = 1) */
 } ft_layered_model;
 
 /* cfg: vocab, max_batch, max_batched_tokens, num_pages, max_context, max_sessions (= state slots), eos, debug_logit_rows
