@@ -119,11 +119,12 @@ def attention_keys(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict,
 
 
 def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict, eps: float, kv) -> torch.Tensor:
-    """Grouped-query attention inside runs of mask.size positions; `kv` = (keys, values) of this or of the lending layer."""
+    """Grouped-query attention inside runs of mask.size positions (no mask: every earlier position); `kv` = (keys, values) of
+    this or of the lending layer."""
     T, H, D = h.shape[0], m["heads"], m["dim"]
     q = rms_unit((h @ w[p + "q"].T).reshape(T, H, D), eps) * w[p + "q.norm"]
     q = rotate_halves(q, torch.arange(T), m.get("rot"))
-    o = attend(q, kv[0], kv[1], visible_chunk(T, int(m["mask"]["size"])), float(m["scale"]))
+    o = attend(q, kv[0], kv[1], visible_chunk(T, int((m.get("mask") or {}).get("size") or max(T, 1))), float(m["scale"]))
     return o @ w[p + "o"].T
 
 
@@ -160,7 +161,7 @@ def conv_window_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m
     k = (rms_unit(k, eps) * w[p + "k.norm"]).reshape(T, G, D)
     pos = torch.arange(T)
     q, k = rotate_halves(q, pos, m.get("rot")), rotate_halves(k, pos, m.get("rot"))
-    o = attend(q, k, v.reshape(T, G, V), visible_window(T, int(m["mask"]["size"])), float(m["scale"]),
+    o = attend(q, k, v.reshape(T, G, V), visible_window(T, int((m.get("mask") or {}).get("size") or max(T, 1))), float(m["scale"]),
                float(m.get("softcap") or 0.0), zero_sink=True)
     return o @ w[p + "o"].T
 
