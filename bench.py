@@ -681,11 +681,11 @@ def main():
                     help="step the engine from Python in the e2e levels instead of ft_engine_start's native thread (A/B)")
     ap.add_argument("--settle", type=float, default=2.0,
                     help="idle seconds between the set-up prefill and the warm-up (power-cap recovery; untimed)")
-    ap.add_argument("--design", default="", choices=["", "gitozen", "gedelorn", "vonedra"],
+    ap.add_argument("--design", default="", choices=["", "gitozen", "gedelorn", "vonedra", "lotinex"],
                     help="prefill / decode throughput of a design of the layered family beside its closest relatives of equal "
                          "size (scripts/bench_layered.py) instead of the default workload")
     ap.add_argument("--sizes", default="", help="--design: comma-separated sizes (s, m)")
-    ap.add_argument("--arms", default="", help="--design: comma-separated arms (vonedra, gedelorn, gitozen, llama)")
+    ap.add_argument("--arms", default="", help="--design: comma-separated arms (lotinex, vonedra, gedelorn, gitozen, llama)")
     args = ap.parse_args()
     if args.design:
         from scripts import bench_layered

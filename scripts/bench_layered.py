@@ -3,6 +3,7 @@
     python bench.py --design gitozen  [--sizes s,m] [--arms gitozen,llama] [--steps K] [--warmup W]
     python bench.py --design gedelorn [--sizes s,m] [--arms gedelorn,gitozen,llama] [--steps K] [--warmup W]
     python bench.py --design vonedra  [--sizes s,m] [--arms vonedra,gedelorn,gitozen,llama] [--steps K] [--warmup W]
+    python bench.py --design lotinex  [--sizes s,m] [--arms lotinex,vonedra,gedelorn,llama] [--steps K] [--warmup W]
 
 For every size all arms get the same width, depth, heads x head size, active feed-forward width (top x expert ff =
 Llama's ffn) and vocabulary.  Gedelorn's closest relative in the framework is Gitozen (the same engine path: stacked
@@ -89,6 +90,30 @@ def vonedra_spec(name, c):
     return spec_from_config(cfg, shapes, name=f"vonedra-{name}")
 
 
+def lotinex_spec(name, c):
+    """Four hyper-connected layers over four streams: attention inside runs of 512 positions (a quarter as many key heads, half
+    of every head rotated) + dense, delta rule + experts, attention over the first layer's keys and values + dense, parallel
+    (window 512 attention with 3-tap convolutions on q, k, v | selective scan of twice the width, 16 states per channel,
+    4 taps) + experts.  Heads x head size and the active feed-forward width as in the other arms."""
+    from fasttalk_llm_microservice_b200.layered import spec_from_config
+    W, H, D = c["width"], c["heads"], c["dim"]
+    G = max(1, H // 4)
+    att = {"dim": D, "heads": H, "kv_heads": G, "mask": {"size": 512}, "rot": {"base": 1e4, "dims": D // 2}, "scale": D ** -0.5, "vdim": D}
+    dlt = {"type": "delta", "mixer": {"conv": 4, "dim": D, "heads": H, "kv_heads": H, "vdim": D}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"conv": 3, "dim": D, "heads": H, "kv_heads": G, "mask": {"size": 512},
+                 "rot": {"base": 1e4, "dims": D // 2, "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048.0, "slow": 1.0}},
+                 "scale": D ** -0.5, "softcap": 50.0, "vdim": D},
+        "right": {"conv": 4, "dt_rank": W // 16, "inner": 2 * W, "state": 16}}}
+    dense = {"ff": c["top"] * c["ff"], "kind": "dense"}
+    moe = {"expert": {"ff": c["ff"]}, "kind": "moe", "router": {"experts": c["experts"], "top": c["top"]}}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": dense}, {**dlt, "mlp": moe},
+              {"type": "attention", "mixer": {**att, "kv_from": 0}, "mlp": dense}, {**par, "mlp": moe}]
+    cfg = {"architecture": "Lotinex", "embedding": {"scale": W ** 0.5}, "layers": layers, "norm": {"eps": 1e-6}, "streams": 4,
+           "vocab": c["vocab"], "width": W}
+    return spec_from_config(cfg, name=f"lotinex-{name}")
+
+
 def llama_spec(name, c):
     from fasttalk_llm_microservice_b200.model_spec import ModelSpec
     return ModelSpec(name=f"llama-{name}", hidden=c["width"], ffn=c["top"] * c["ff"], layers=len(c["order"]),
@@ -151,10 +176,11 @@ def run(args) -> None:
         c = SIZES[name]
         row = {"config": c}
         design = getattr(args, "design", "") or "gitozen"
-        default_arms = {"vonedra": "vonedra,gedelorn,gitozen,llama", "gedelorn": "gedelorn,gitozen,llama"}.get(design, "gitozen,llama")
+        default_arms = {"lotinex": "lotinex,vonedra,gedelorn,llama", "vonedra": "vonedra,gedelorn,gitozen,llama",
+                        "gedelorn": "gedelorn,gitozen,llama"}.get(design, "gitozen,llama")
         for arm in (getattr(args, "arms", "") or default_arms).split(","):
-            if arm in ("gitozen", "gedelorn", "vonedra"):
-                spec = {"gitozen": gitozen_spec, "gedelorn": gedelorn_spec, "vonedra": vonedra_spec}[arm](name, c)
+            if arm in ("gitozen", "gedelorn", "vonedra", "lotinex"):
+                spec = {"gitozen": gitozen_spec, "gedelorn": gedelorn_spec, "vonedra": vonedra_spec, "lotinex": lotinex_spec}[arm](name, c)
                 w = init_layered(spec, seed=0, device="cuda")
             else:
                 spec = llama_spec(name, c)
