@@ -784,7 +784,8 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         }
     } else if (c.kind == FT_BRANCH_SELECTIVE_SCAN) {
         // x through its convolution (bias, SiLU) -> (low | B | C) = W_x x -> dt_raw = W_dt low -> the scan, gated by silu(z)
-        const int inner = c.heads, N = c.dim, R = c.dt_rank, nl = R + 2 * N;
+        const int inner = c.heads, N = c.dim, R = c.dt_rank, nl = c.x_rows > 0 ? c.x_rows : R + 2 * N;
+        const int kdt = c.x_rows > 0 ? c.x_rows : R;       // columns of w_dt
         SpaceArgs s;
         s.proj = L.proj; s.ldp = ld; s.o_x = c.o_v; s.channels = inner; s.taps = c.conv; s.heads = 0; s.act = 1;
         s.conv_w = c.conv_w; s.conv_b = c.conv_b; s.xbc = L.bv; s.state = L.state; s.slot_stride = (long long)L.slot_stride;
@@ -793,10 +794,15 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         FT_TRY(launch_space_prep(s, T, b.n_req, st));
         launched(2);
         FT_TRY(dense(e, L.bv, nullptr, nullptr, c.w_x, L.b1, T, nl, inner));
-        LinearArgs dtp;                     // the step sizes' pre-activation from the first R columns of the low-rank row
-        dtp.A = L.b1; dtp.lda = nl; dtp.W = (const __nv_bfloat16*)c.w_dt; dtp.ldw = R; dtp.C = L.b2; dtp.ldc = inner;
-        dtp.M = T; dtp.N = inner; dtp.K = R;
-        FT_TRY(launch_linear(dtp, T, st));
+        // the step sizes' pre-activation from the first R columns of the low-rank row (the whole row when w_dt is padded)
+        if (kdt == nl) {
+            FT_TRY(dense(e, L.b1, nullptr, nullptr, c.w_dt, L.b2, T, inner, nl));
+        } else {
+            LinearArgs dtp;
+            dtp.A = L.b1; dtp.lda = nl; dtp.W = (const __nv_bfloat16*)c.w_dt; dtp.ldw = kdt; dtp.C = L.b2; dtp.ldc = inner;
+            dtp.M = T; dtp.N = inner; dtp.K = kdt;
+            FT_TRY(launch_linear(dtp, T, st));
+        }
         ScanArgs sc;
         sc.x = L.bv; sc.ldx = inner; sc.dt_raw = L.b2; sc.ldd = inner; sc.B = L.b1 + R; sc.C = L.b1 + R + N; sc.ldbc = nl;
         sc.z = L.proj + c.o_z; sc.ldz = ld; sc.dt_bias = c.dt_bias; sc.a_log = c.a_log; sc.skip = c.skip; sc.out = L.bfin;
@@ -1770,7 +1776,8 @@ static int engine_init_layered(Engine* e) {
                     ll.br_x_off[k] = L.slot_stride;
                     L.slot_stride += (size_t)c.heads * (size_t)(c.conv - 1);
                     br_v = std::max(br_v, (size_t)c.heads);
-                    buf = std::max(buf, std::max((size_t)c.heads, (size_t)c.dt_rank + 2 * c.dim));
+                    FT_REQUIRE(c.x_rows == 0 || c.x_rows >= c.dt_rank + 2 * c.dim, "engine: layer %d branch %d: x_rows below the low-rank row", l, k);
+                    buf = std::max(buf, std::max((size_t)c.heads, (size_t)std::max(c.x_rows, c.dt_rank + 2 * c.dim)));
                     L.n_stateful++;
                 } else {
                     FT_REQUIRE(false, "engine: layer %d branch %d has an unknown kind %d", l, k, c.kind);

@@ -143,62 +143,94 @@ __global__ void __launch_bounds__(256) scaled_rows_kernel(const float* __restric
 }
 
 // LPC lanes (a power of two, neighbours in a warp) share a channel; lane s of them holds states s, s + LPC, s + 2 LPC, ...
-// (at most kScanKeep each).  What a token brings — dt, x, z, B, C — does not depend on the state, so the loads of the next
-// token are issued before the arithmetic of this one.
-constexpr int kScanThreads = 128, kScanKeep = 8;
+// (at most kScanKeep each), so a CTA of 128 threads owns 128 / LPC channels.  A request's tokens come in chunks of kScanChunk:
+// what a chunk brings — dt, x, z of the CTA's channels, B and C — is copied asynchronously into one of two shared-memory
+// buffers while the chunk before it is computed.  Per chunk: the step sizes pass softplus in place (all threads), then the
+// tokens in order (the state is the only dependence from token to token; a channel's partial read-outs meet by shuffles and
+// land where its dt was), then skip, gate and the store, again by all threads with the channels along the lanes.
+constexpr int kScanThreads = 128, kScanKeep = 8, kScanChunk = 16;
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
 __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(ScanArgs a, int lpc) {
+    extern __shared__ __align__(16) float ssm[];
     const int r = blockIdx.y;
     const int start = a.req_start[r], n_tok = a.req_start[r + 1] - start;
     if (n_tok <= 0) return;
-    const int per = kScanThreads / lpc;
-    const int c = blockIdx.x * per + threadIdx.x / lpc, s = threadIdx.x % lpc;
+    const int per = kScanThreads / lpc, N = a.N;
+    const int c0 = blockIdx.x * per, ci = threadIdx.x / lpc, s = threadIdx.x % lpc;
+    const int c = c0 + ci;
     const bool live = c < a.channels;
     const int cc = live ? c : a.channels - 1;
-    float* Sg = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)cc * a.N;
+    const int n_ch = min(per, a.channels - c0);              // channels of this CTA that exist
+    const int stage_f = kScanChunk * (3 * per + 2 * N);
+    float* Sg = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)cc * N;
     const bool fresh = a.req_pos0[r] == 0;
     float S[kScanKeep], A[kScanKeep];
 #pragma unroll
     for (int i = 0; i < kScanKeep; ++i) {
         const int n = s + lpc * i;
-        const bool ok = n < a.N;
+        const bool ok = n < N;
         S[i] = ok && !fresh ? Sg[n] : 0.f;
-        A[i] = ok ? -expf(a.a_log[(size_t)cc * a.N + n]) : 0.f;
+        A[i] = ok ? -expf(a.a_log[(size_t)cc * N + n]) : 0.f;
     }
-    const float bias = a.dt_bias[cc], skip = a.skip[cc];
-    float dtr, x, z, Bn[kScanKeep], Cn[kScanKeep];
-    auto fetch = [&](int t) {
-        dtr = a.dt_raw[(size_t)t * a.ldd + cc];
-        x = a.x[(size_t)t * a.ldx + cc];
-        z = a.z[(size_t)t * a.ldz + cc];
-#pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) {
-            const int n = s + lpc * i;
-            Bn[i] = n < a.N ? a.B[(size_t)t * a.ldbc + n] : 0.f;
-            Cn[i] = n < a.N ? a.C[(size_t)t * a.ldbc + n] : 0.f;
+    auto stage = [&](int ch, float* buf) {
+        const int t0 = start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
+        float *sdt = buf, *sx = sdt + kScanChunk * per, *sz = sx + kScanChunk * per, *sB = sz + kScanChunk * per, *sC = sB + kScanChunk * N;
+        for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
+            const int k = i / n_ch, j = i - k * n_ch;
+            const size_t t = (size_t)(t0 + k);
+            cp_async4(sdt + k * per + j, a.dt_raw + t * a.ldd + c0 + j);
+            cp_async4(sx + k * per + j, a.x + t * a.ldx + c0 + j);
+            cp_async4(sz + k * per + j, a.z + t * a.ldz + c0 + j);
         }
+        for (int i = threadIdx.x; i < nt * N; i += kScanThreads) {
+            const int k = i / N, n = i - k * N;
+            const size_t t = (size_t)(t0 + k);
+            cp_async4(sB + k * N + n, a.B + t * a.ldbc + n);
+            cp_async4(sC + k * N + n, a.C + t * a.ldbc + n);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    fetch(start);
-    for (int k = 0; k < n_tok; ++k) {
-        const int t = start + k;
-        const float dt = softplus_h(dtr + bias), x0 = x, z0 = z, dx = dt * x;
-        float b0[kScanKeep], c0[kScanKeep];
-#pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) { b0[i] = Bn[i]; c0[i] = Cn[i]; }
-        if (k + 1 < n_tok) fetch(t + 1);
-        float y = 0.f;
-#pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) {
-            S[i] = fmaf(expf(dt * A[i]), S[i], dx * b0[i]);
-            y = fmaf(S[i], c0[i], y);
+    const int n_chunks = (n_tok + kScanChunk - 1) / kScanChunk;
+    stage(0, ssm);
+    for (int ch = 0; ch < n_chunks; ++ch) {
+        float* buf = ssm + (ch & 1) * stage_f;
+        float *sdt = buf, *sx = sdt + kScanChunk * per, *sz = sx + kScanChunk * per, *sB = sz + kScanChunk * per, *sC = sB + kScanChunk * N;
+        const int t0 = start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();                                     // chunk ch has landed; nobody still reads the other buffer
+        if (ch + 1 < n_chunks) stage(ch + 1, ssm + ((ch + 1) & 1) * stage_f);
+        for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
+            const int k = i / n_ch, j = i - k * n_ch;
+            sdt[k * per + j] = softplus_h(sdt[k * per + j] + a.dt_bias[c0 + j]);
         }
-        for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
-        if (live && s == 0) a.out[(size_t)t * a.channels + c] = fmaf(skip, x0, y) * silu_h(z0);
+        __syncthreads();
+        for (int k = 0; k < nt; ++k) {
+            const float dt = sdt[k * per + ci], dx = dt * sx[k * per + ci];
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < kScanKeep; ++i) {
+                const int n = s + lpc * i;
+                if (n < N) {
+                    S[i] = fmaf(expf(dt * A[i]), S[i], dx * sB[k * N + n]);
+                    y = fmaf(S[i], sC[k * N + n], y);
+                }
+            }
+            for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+            if (s == 0) sdt[k * per + ci] = y;               // every lane of the channel has read dt before the shuffles end
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
+            const int k = i / n_ch, j = i - k * n_ch;
+            a.out[(size_t)(t0 + k) * a.channels + c0 + j] = fmaf(a.skip[c0 + j], sx[k * per + j], sdt[k * per + j]) * silu_h(sz[k * per + j]);
+        }
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < kScanKeep; ++i) {
             const int n = s + lpc * i;
-            if (n < a.N) Sg[n] = S[i];
+            if (n < N) Sg[n] = S[i];
         }
     }
 }
@@ -237,8 +269,11 @@ int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream) {
     while (lpc < 32 && (long long)n_req * ((a.channels * lpc + kScanThreads - 1) / kScanThreads) < 148 && lpc < a.N) lpc <<= 1;
     while (lpc * kScanKeep < a.N) lpc <<= 1;
     const int per = kScanThreads / lpc;
+    const size_t smem = (size_t)2 * kScanChunk * (3 * per + 2 * a.N) * 4;
+    if (smem > 48 * 1024)
+        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((a.channels + per - 1) / per, n_req);
-    selective_scan_kernel<<<grid, kScanThreads, 0, stream>>>(a, lpc);
+    selective_scan_kernel<<<grid, kScanThreads, smem, stream>>>(a, lpc);
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -713,7 +713,7 @@ class BranchDesc(C.Structure):
         ("w_uq", C.c_void_p), ("w_uk_t", C.c_void_p), ("w_uv", C.c_void_p), ("q_norm", C.c_void_p), ("kv_norm", C.c_void_p),
         ("rot_half", C.c_int), ("chunked", C.c_int), ("kv_lender", C.c_int), ("rot_mag", C.c_float),
         ("q_gain", C.c_void_p), ("k_gain", C.c_void_p), ("out_gain", C.c_void_p),
-        ("dt_rank", C.c_int), ("w_x", C.c_void_p), ("w_dt", C.c_void_p),
+        ("dt_rank", C.c_int), ("w_x", C.c_void_p), ("w_dt", C.c_void_p), ("x_rows", C.c_int),
     ]
 
 
@@ -942,7 +942,14 @@ def _pack_hyper_layer(spec: LayeredSpec, i: int, l: LayerSpec, w: Dict[str, torc
             c.o_z = c.o_v + C_
             c.conv, c.dt_rank = b.conv, b.dt_rank
             c.conv_w, c.conv_b = vec(q + "conv"), vec(q + "conv.b")
-            c.w_x, c.w_dt = dev(w[q + "x"]).data_ptr(), dev(w[q + "dt"]).data_ptr()
+            # the low-rank projection padded with zero rows to whole tensor-core tiles; the step-size projection reads the whole
+            # padded row, its columns beyond dt_rank are zero
+            rows = (b.dt_rank + 2 * b.dim + 127) // 128 * 128
+            w_x = torch.zeros(rows, C_, dtype=torch.bfloat16, device=device)
+            w_x[:b.dt_rank + 2 * b.dim] = w[q + "x"].to(device)
+            w_dt = torch.zeros(C_, rows, dtype=torch.bfloat16, device=device)
+            w_dt[:, :b.dt_rank] = w[q + "dt"].to(device)
+            c.w_x, c.w_dt, c.x_rows = dev(w_x).data_ptr(), dev(w_dt).data_ptr(), rows
             c.dt_bias, c.a_log, c.skip = vec(q + "dt.b"), vec(q + "A_log"), vec(q + "D")
     d.ff_kind = FF_NONE
     if l.ff_kind:

@@ -306,6 +306,8 @@ typedef struct {
     int dt_rank;
     const void* w_x;           /* bf16 [dt_rank + 2 * dim][heads] */
     const void* w_dt;          /* bf16 [heads][dt_rank] */
+    int x_rows;                /* 0, or the rows of w_x when it is padded with zero rows to whole GEMM tiles; w_dt is then
+                                  [heads][x_rows] with zeros beyond column dt_rank (it reads the whole low-rank row) */
 } ft_branch_desc;
 
 typedef struct {
