@@ -184,8 +184,8 @@ struct Layered {
     float* state = nullptr;
     size_t slot_stride = 0;            // floats per state slot
     int n_stateful = 0;                // layers whose mixer carries state from token to token
-    int ld_proj = 0, top_max = 0;
-    float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr,
+    int ld_proj = 0, top_max = 0, scan_ws_rows = 0;
+    float *hn = nullptr, *proj = nullptr, *b1 = nullptr, *b2 = nullptr, *b3 = nullptr, *b4 = nullptr, *beta = nullptr, *scan_ws = nullptr,
           *attn_part = nullptr, *mix = nullptr, *act = nullptr, *eout = nullptr, *wts = nullptr, *xlast = nullptr;
     // branch mixers and sandwich layers: queries, prepared values, rule outputs, read-out, (decay, input) pairs, log gates,
     // denominator floors, the second branch's projection, feed-forward halves, router logits
@@ -808,7 +808,7 @@ static int run_branch(Engine* e, const Batch& b, const LayeredLayer& ll, int k, 
         sc.z = L.proj + c.o_z; sc.ldz = ld; sc.dt_bias = c.dt_bias; sc.a_log = c.a_log; sc.skip = c.skip; sc.out = L.bfin;
         sc.state = L.state; sc.slot_stride = (long long)L.slot_stride; sc.s_off = (long long)ll.br_s_off[k];
         sc.req_start = d + m.o_xstart; sc.req_pos0 = d + m.o_xpos0; sc.req_slot = d + m.o_xslot;
-        sc.channels = inner; sc.N = N;
+        sc.channels = inner; sc.N = N; sc.rows = T; sc.ws = L.scan_ws; sc.ws_rows = L.scan_ws_rows;
         FT_TRY(launch_selective_scan(sc, b.n_req, st));
         launched(2);
     } else {
@@ -1628,7 +1628,7 @@ static int engine_init_layered(Engine* e) {
 
     // sizes over all layers; places of each layer in the latent cache and in a state slot
     size_t cache_floats = 0, buf = 1, act_cols = 1;
-    size_t kv_floats = 0, br_q = 0, br_v = 0, br_o = 0, br_fin = 0, br_heads = 0, e_max_s = 1;
+    size_t kv_floats = 0, br_q = 0, br_v = 0, br_o = 0, br_fin = 0, br_heads = 0, e_max_s = 1, scan_cn = 0;
     int n_in_max = 1, top_max = 1, heads_max = 1, rank_max = 0;
     size_t vfirst_cols = 0, lstage_cols = 0;
     bool use_hist = false;
@@ -1776,6 +1776,7 @@ static int engine_init_layered(Engine* e) {
                     ll.br_x_off[k] = L.slot_stride;
                     L.slot_stride += (size_t)c.heads * (size_t)(c.conv - 1);
                     br_v = std::max(br_v, (size_t)c.heads);
+                    scan_cn = std::max(scan_cn, (size_t)c.heads * (size_t)(c.dim + 1));
                     FT_REQUIRE(c.x_rows == 0 || c.x_rows >= c.dt_rank + 2 * c.dim, "engine: layer %d branch %d: x_rows below the low-rank row", l, k);
                     buf = std::max(buf, std::max((size_t)c.heads, (size_t)std::max(c.x_rows, c.dt_rank + 2 * c.dim)));
                     L.n_stateful++;
@@ -1875,6 +1876,10 @@ static int engine_init_layered(Engine* e) {
     }
     FT_TRY(alloc(&L.b1, T * buf * 4));
     FT_TRY(alloc(&L.b2, T * buf * 4));
+    if (scan_cn > 0) {                  // what the segments of a long request leave behind for one another
+        L.scan_ws_rows = selective_scan_ws_rows((int)T);
+        FT_TRY(alloc(&L.scan_ws, (size_t)L.scan_ws_rows * scan_cn * 4));
+    }
     FT_TRY(alloc(&L.b3, T * buf * 4));
     FT_TRY(alloc(&L.b4, T * buf * 4));
     FT_TRY(alloc(&L.beta, T * heads_max * 4));
@@ -1923,7 +1928,7 @@ static void engine_free(Engine* e) {
     cudaFree(e->x16_xn); cudaFree(e->x16_attn); cudaFree(e->x16_act);
     if (e->lay) {
         Layered& L = *e->lay;
-        cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2);
+        cudaFree(L.lat_cache); cudaFree(L.lat_cache16); cudaFree(L.state); cudaFree(L.hn); cudaFree(L.proj); cudaFree(L.b1); cudaFree(L.b2); cudaFree(L.scan_ws);
         cudaFree(L.b3); cudaFree(L.b4); cudaFree(L.beta); cudaFree(L.attn_part); cudaFree(L.mix); cudaFree(L.act); cudaFree(L.eout);
         cudaFree(L.kv_cache); cudaFree(L.bq); cudaFree(L.bv); cudaFree(L.bo); cudaFree(L.bfin); cudaFree(L.ab); cudaFree(L.gates);
         cudaFree(L.hist); cudaFree(L.v_first); cudaFree(L.lstage); cudaFree(L.resid2); cudaFree(L.streams);

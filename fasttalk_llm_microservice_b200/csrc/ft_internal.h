@@ -396,7 +396,11 @@ struct ScanArgs {
     long long slot_stride = 0, s_off = 0;
     const int *req_start = nullptr, *req_pos0 = nullptr, *req_slot = nullptr;
     int channels = 0, N = 0;
+    int rows = 0;                                 // T, all requests' tokens of the step
+    float* ws = nullptr;                          // room for long requests cut into segments, or null (every request in
+    int ws_rows = 0;                              // order then): ws_rows x channels x (N + 1) floats
 };
+int selective_scan_ws_rows(int rows);             // the ws_rows a step of this many rows needs
 int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream);
 
 // ---- sampling.cu

@@ -143,20 +143,36 @@ __global__ void __launch_bounds__(256) scaled_rows_kernel(const float* __restric
 }
 
 // LPC lanes (a power of two, neighbours in a warp) share a channel; lane s of them holds states s, s + LPC, s + 2 LPC, ...
-// (at most kScanKeep each), so a CTA of 128 threads owns 128 / LPC channels.  A request's tokens come in chunks of kScanChunk:
-// what a chunk brings — dt, x, z of the CTA's channels, B and C — is copied asynchronously into one of two shared-memory
-// buffers while the chunk before it is computed.  Per chunk: the step sizes pass softplus in place (all threads), then the
-// tokens in order (the state is the only dependence from token to token; a channel's partial read-outs meet by shuffles and
-// land where its dt was), then skip, gate and the store, again by all threads with the channels along the lanes.
-constexpr int kScanThreads = 128, kScanKeep = 8, kScanChunk = 16;
+// (at most kScanKeep each), so a CTA of 128 threads owns 128 / LPC channels.  A request's tokens are cut into segments of
+// seg_len (a multiple of the chunk), blockIdx.z names the segment, and the recurrence being linear in S lets the segments
+// run side by side in two launches:
+//   phase 0  segment 0 of every request runs from the slot's state (zero for a fresh sequence) and writes its outputs; a
+//            request of one segment ends here (its state returns to the slot).  Every other segment but the last runs from
+//            ZERO and writes nothing but what it leaves behind: L_p[c][n], its own contribution to the state at its end, and
+//            d_p[c], the sum of its step sizes (the decay of a whole segment is exp(A[c][n] d_p[c])).  Segment 0 leaves the
+//            true state at its end as L_0
+//   phase 1  segment p >= 1 folds S = L_0, S <- exp(A d_q) S + L_q for q = 1 .. p-1, runs its tokens from there and writes
+//            their outputs; the last one returns the state to the slot
+// A step without a long request is phase 0 alone.  The workspace row of a full segment is (its first row) / seg_len, which no
+// two full segments share.  Inside a segment the tokens come in chunks of kScanChunk: what a chunk brings — dt, x, z of the
+// CTA's channels, B and C — is copied asynchronously into one of two shared-memory buffers while the chunk before it is
+// computed.  Per chunk: the step sizes pass softplus in place (all threads), then the tokens in order (the state is the only
+// dependence from token to token; a channel's partial read-outs meet by shuffles and land where its dt was), then skip, gate
+// and the store, again by all threads with the channels along the lanes.  Decays are 2^(dt A log2(e)).
+constexpr int kScanThreads = 128, kScanKeep = 8, kScanChunk = 16, kScanSeg = 128;
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
-__global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(ScanArgs a, int lpc) {
+template <int PHASE>
+__global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArgs a, int lpc, int seg_len) {
     extern __shared__ __align__(16) float ssm[];
-    const int r = blockIdx.y;
-    const int start = a.req_start[r], n_tok = a.req_start[r + 1] - start;
-    if (n_tok <= 0) return;
+    const int r = blockIdx.y, seg = blockIdx.z + PHASE;
+    const int start = a.req_start[r], n_req_tok = a.req_start[r + 1] - start;
+    if (n_req_tok <= 0) return;
+    const int n_seg = (n_req_tok + seg_len - 1) / seg_len;
+    if (PHASE == 0 ? (seg > 0 && seg >= n_seg - 1) : seg >= n_seg) return;
+    const bool emit = PHASE == 1 || seg == 0, last = seg == n_seg - 1;
+    const int seg_start = start + seg * seg_len, n_tok = min(seg_len, n_req_tok - seg * seg_len);
     const int per = kScanThreads / lpc, N = a.N;
     const int c0 = blockIdx.x * per, ci = threadIdx.x / lpc, s = threadIdx.x % lpc;
     const int c = c0 + ci;
@@ -165,39 +181,64 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(ScanArgs a
     const int n_ch = min(per, a.channels - c0);              // channels of this CTA that exist
     const int stage_f = kScanChunk * (3 * per + 2 * N);
     float* Sg = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)cc * N;
-    const bool fresh = a.req_pos0[r] == 0;
+    float* Lw = a.ws + (size_t)a.ws_rows * a.channels * N;    // behind the L rows: the segments' summed step sizes
     float S[kScanKeep], A[kScanKeep];
 #pragma unroll
     for (int i = 0; i < kScanKeep; ++i) {
         const int n = s + lpc * i;
-        const bool ok = n < N;
-        S[i] = ok && !fresh ? Sg[n] : 0.f;
-        A[i] = ok ? -expf(a.a_log[(size_t)cc * N + n]) : 0.f;
+        A[i] = n < N ? -expf(a.a_log[(size_t)cc * N + n]) * 1.4426950408889634f : 0.f;
+        S[i] = 0.f;
+    }
+    if (seg == 0) {
+        if (a.req_pos0[r] != 0) {
+#pragma unroll
+            for (int i = 0; i < kScanKeep; ++i) {
+                const int n = s + lpc * i;
+                if (n < N) S[i] = Sg[n];
+            }
+        }
+    } else if (PHASE == 1) {
+        const size_t q0 = (size_t)(start / seg_len);         // segment 0's row; the later full segments follow it in order
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) {
+            const int n = s + lpc * i;
+            if (n < N) S[i] = a.ws[(q0 * a.channels + cc) * N + n];
+        }
+        for (int p = 1; p < seg; ++p) {
+            const size_t q = (size_t)((start + p * seg_len) / seg_len);
+            const float d = Lw[q * a.channels + cc];
+#pragma unroll
+            for (int i = 0; i < kScanKeep; ++i) {
+                const int n = s + lpc * i;
+                if (n < N) S[i] = fmaf(exp2f(d * A[i]), S[i], a.ws[(q * a.channels + cc) * N + n]);
+            }
+        }
     }
     auto stage = [&](int ch, float* buf) {
-        const int t0 = start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
+        const int t0 = seg_start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
         float *sdt = buf, *sx = sdt + kScanChunk * per, *sz = sx + kScanChunk * per, *sB = sz + kScanChunk * per, *sC = sB + kScanChunk * N;
         for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
             const int k = i / n_ch, j = i - k * n_ch;
             const size_t t = (size_t)(t0 + k);
             cp_async4(sdt + k * per + j, a.dt_raw + t * a.ldd + c0 + j);
             cp_async4(sx + k * per + j, a.x + t * a.ldx + c0 + j);
-            cp_async4(sz + k * per + j, a.z + t * a.ldz + c0 + j);
+            if (emit) cp_async4(sz + k * per + j, a.z + t * a.ldz + c0 + j);
         }
         for (int i = threadIdx.x; i < nt * N; i += kScanThreads) {
             const int k = i / N, n = i - k * N;
             const size_t t = (size_t)(t0 + k);
             cp_async4(sB + k * N + n, a.B + t * a.ldbc + n);
-            cp_async4(sC + k * N + n, a.C + t * a.ldbc + n);
+            if (emit) cp_async4(sC + k * N + n, a.C + t * a.ldbc + n);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int n_chunks = (n_tok + kScanChunk - 1) / kScanChunk;
+    float dsum = 0.f;
     stage(0, ssm);
     for (int ch = 0; ch < n_chunks; ++ch) {
         float* buf = ssm + (ch & 1) * stage_f;
         float *sdt = buf, *sx = sdt + kScanChunk * per, *sz = sx + kScanChunk * per, *sB = sz + kScanChunk * per, *sC = sB + kScanChunk * N;
-        const int t0 = start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
+        const int t0 = seg_start + ch * kScanChunk, nt = min(kScanChunk, n_tok - ch * kScanChunk);
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();                                     // chunk ch has landed; nobody still reads the other buffer
         if (ch + 1 < n_chunks) stage(ch + 1, ssm + ((ch + 1) & 1) * stage_f);
@@ -206,32 +247,62 @@ __global__ void __launch_bounds__(kScanThreads) selective_scan_kernel(ScanArgs a
             sdt[k * per + j] = softplus_h(sdt[k * per + j] + a.dt_bias[c0 + j]);
         }
         __syncthreads();
-        for (int k = 0; k < nt; ++k) {
+        auto token = [&](int k) -> float {
             const float dt = sdt[k * per + ci], dx = dt * sx[k * per + ci];
+            dsum += dt;
             float y = 0.f;
 #pragma unroll
             for (int i = 0; i < kScanKeep; ++i) {
                 const int n = s + lpc * i;
                 if (n < N) {
-                    S[i] = fmaf(expf(dt * A[i]), S[i], dx * sB[k * N + n]);
-                    y = fmaf(S[i], sC[k * N + n], y);
+                    S[i] = fmaf(exp2f(dt * A[i]), S[i], dx * sB[k * N + n]);
+                    if (emit) y = fmaf(S[i], sC[k * N + n], y);
                 }
             }
-            for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
-            if (s == 0) sdt[k * per + ci] = y;               // every lane of the channel has read dt before the shuffles end
+            if (emit)
+                for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+            return y;
+        };
+        if (nt == kScanChunk) {                              // a whole chunk: four tokens at a time with their read-outs in
+#pragma unroll 1                                             // registers, so that their loads and shuffles overlap
+            for (int k0 = 0; k0 < kScanChunk; k0 += 4) {
+                float y[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) y[k] = token(k0 + k);
+                if (emit && s == 0) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) sdt[(k0 + k) * per + ci] = y[k];
+                }
+            }
+        } else {
+            for (int k = 0; k < nt; ++k) {
+                const float y = token(k);
+                if (emit && s == 0) sdt[k * per + ci] = y;   // every lane of the channel has read dt before the shuffles end
+            }
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
-            const int k = i / n_ch, j = i - k * n_ch;
-            a.out[(size_t)(t0 + k) * a.channels + c0 + j] = fmaf(a.skip[c0 + j], sx[k * per + j], sdt[k * per + j]) * silu_h(sz[k * per + j]);
+        if (emit) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < nt * n_ch; i += kScanThreads) {
+                const int k = i / n_ch, j = i - k * n_ch;
+                a.out[(size_t)(t0 + k) * a.channels + c0 + j] = fmaf(a.skip[c0 + j], sx[k * per + j], sdt[k * per + j]) * silu_h(sz[k * per + j]);
+            }
         }
     }
-    if (live) {
+    if (!live) return;
+    if (last) {
 #pragma unroll
         for (int i = 0; i < kScanKeep; ++i) {
             const int n = s + lpc * i;
             if (n < N) Sg[n] = S[i];
         }
+    } else if (PHASE == 0) {
+        const size_t q = (size_t)(seg_start / seg_len);
+#pragma unroll
+        for (int i = 0; i < kScanKeep; ++i) {
+            const int n = s + lpc * i;
+            if (n < N) a.ws[(q * a.channels + c) * N + n] = S[i];
+        }
+        if (s == 0) Lw[q * a.channels + c] = dsum;
     }
 }
 
@@ -259,22 +330,35 @@ int launch_scaled_rows(const float* src, const float* wt, const int* slot_pos, i
     return 0;
 }
 
+int selective_scan_ws_rows(int rows) { return rows / kScanSeg + 1; }
+
 int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream) {
     FT_REQUIRE(a.channels >= 1 && a.N >= 1 && a.N <= 32 * kScanKeep, "selective scan: 1 to %d states per channel (got %d)",
                32 * kScanKeep, a.N);
     FT_REQUIRE(a.x && a.dt_raw && a.B && a.C && a.z && a.dt_bias && a.a_log && a.skip && a.out && a.state, "selective scan: missing operands");
+    FT_REQUIRE(n_req >= 1 && a.rows >= n_req, "selective scan: %d rows for %d requests", a.rows, n_req);
+    // the longest request has at most rows - (n_req - 1) tokens; segments only when the workspace holds their rows
+    int n_seg = (a.rows - (n_req - 1) + kScanSeg - 1) / kScanSeg;
+    if (!a.ws || a.ws_rows < selective_scan_ws_rows(a.rows)) n_seg = 1;
+    const int seg_len = n_seg > 1 ? kScanSeg : a.rows + 1;
     // lanes per channel: about four states per lane; more lanes when the grid would leave SMs idle
     int lpc = 1;
     while (lpc < 32 && lpc * 4 < a.N) lpc <<= 1;
-    while (lpc < 32 && (long long)n_req * ((a.channels * lpc + kScanThreads - 1) / kScanThreads) < 148 && lpc < a.N) lpc <<= 1;
+    while (lpc < 32 && (long long)n_req * n_seg * ((a.channels * lpc + kScanThreads - 1) / kScanThreads) < 148 && lpc < a.N) lpc <<= 1;
     while (lpc * kScanKeep < a.N) lpc <<= 1;
     const int per = kScanThreads / lpc;
     const size_t smem = (size_t)2 * kScanChunk * (3 * per + 2 * a.N) * 4;
-    if (smem > 48 * 1024)
-        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((a.channels + per - 1) / per, n_req);
-    selective_scan_kernel<<<grid, kScanThreads, smem, stream>>>(a, lpc);
+    if (smem > 48 * 1024) {
+        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    const unsigned cx = (a.channels + per - 1) / per;
+    selective_scan_kernel<0><<<dim3(cx, n_req, std::max(1, n_seg - 1)), kScanThreads, smem, stream>>>(a, lpc, seg_len);
     FT_CHECK_CUDA(cudaGetLastError());
+    if (n_seg > 1) {
+        selective_scan_kernel<1><<<dim3(cx, n_req, n_seg - 1), kScanThreads, smem, stream>>>(a, lpc, seg_len);
+        FT_CHECK_CUDA(cudaGetLastError());
+    }
     return 0;
 }
 

@@ -342,6 +342,35 @@ def test_recurrent_layers_remember_a_far_write():
             eng.close()
 
 
+@pytest.mark.parametrize("slow", [False, True], ids=["fast-decay", "slow-decay"])
+def test_selective_scan_of_long_portions_runs_in_segments(slow):
+    """The scan kernel cuts a portion of more than 128 tokens into segments that run side by side and are joined through the
+    decay of whole segments.  Portions of two to six segments, from a zero state and from a carried one, beside a second
+    request whose rows start off a segment's multiple; state counts that are no power of two and that exceed a warp's lanes."""
+    def tweak(w):
+        for k in list(w):
+            if k.endswith("right.dt.b") or k.endswith("right.A_log"):
+                w[k] = (w[k].float() - 4.0).to(torch.bfloat16)
+    for inner, state in ((40, 9), (24, 37)):
+        spec, w = make([layer(parallel(left_side(size=4), inner=inner, state=state, dt_rank=5), dense(ff=24))], width=48, seed=41,
+                       tweak=tweak if slow else None)
+        eng = engine(spec, w, max_batched_tokens=1024, max_context=1024, num_pages=32, debug_logit_rows=1024)
+        try:
+            a, b = tokens_of(spec, 800, 42), tokens_of(spec, 300, 43)
+            ra, rb = oracle_logits(spec, w, a), oracle_logits(spec, w, b)
+            g1 = eng.feed([("a", a[:130], list(range(130)))])
+            g2 = eng.feed([("a", a[130:643], list(range(513))), ("b", b[:140], list(range(140)))])
+            g3 = eng.feed([("b", b[140:], list(range(160))), ("a", a[643:], list(range(157)))])
+            ga = np.concatenate([g1, g2[:513], g3[160:]])
+            gb = np.concatenate([g2[513:], g3[:160]])
+            assert rel(ga, ra) < TOL and rel(gb, rb) < TOL
+            eng.close_session("a")
+            whole = eng.feed([("w", a, list(range(len(a))))])
+            assert rel(whole, ra) < TOL and rel(whole, ga) < 2e-5
+        finally:
+            eng.close()
+
+
 def test_first_tokens_and_long_decoding():
     spec, w = make(MIXED, seed=19)
     eng = engine(spec, w)
