@@ -13,6 +13,7 @@
 #include "ft_internal.h"
 
 #include <algorithm>
+#include <cstdint>
 
 namespace ft {
 namespace {
@@ -37,13 +38,57 @@ __device__ __forceinline__ float cta_total(float v, float* red) {      // red: >
 
 constexpr int kMaxStreams = 16;
 
-// MS: streams a thread keeps in registers (the arrays are indexed by unrolled loops)
-template <int MS>
+// V consecutive columns of a row at once: 16-byte loads and stores of fp32 (8-byte ones of bf16) when V == 4.
+template <int V>
+__device__ __forceinline__ void ld_cols(float (&d)[V], const float* p) {
+    if constexpr (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+    } else {
+        d[0] = *p;
+    }
+}
+template <int V>
+__device__ __forceinline__ void st_cols(float* p, const float (&d)[V]) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(d[0], d[1], d[2], d[3]);
+    else *p = d[0];
+}
+template <int V>
+__device__ __forceinline__ void ld_cols_bf16(float (&d)[V], const __nv_bfloat16* p) {
+    if constexpr (V == 4) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        d[0] = __low2float(a); d[1] = __high2float(a); d[2] = __low2float(b); d[3] = __high2float(b);
+    } else {
+        d[0] = __bfloat162float(*p);
+    }
+}
+template <int V>
+__device__ __forceinline__ void st_planes(__nv_bfloat16* hi, __nv_bfloat16* lo, const float (&d)[V]) {
+    __nv_bfloat16 h[V], l[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        h[i] = __float2bfloat16_rn(d[i]);
+        l[i] = __float2bfloat16_rn(d[i] - __bfloat162float(h[i]));
+    }
+    if constexpr (V == 4) {
+        *reinterpret_cast<uint2*>(hi) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(lo) = *reinterpret_cast<const uint2*>(l);
+    } else {
+        *hi = h[0];
+        *lo = l[0];
+    }
+}
+
+// MS: streams a thread keeps in registers (the arrays are indexed by unrolled loops); V: columns per thread and pass (4 when
+// the width is a multiple of four and every row starts on 16 bytes)
+template <int MS, int V>
 __global__ void __launch_bounds__(256) hyper_joint_kernel(HyperArgs a) {
     __shared__ float red[33];
     __shared__ float smix[kMaxStreams * kMaxStreams], sout[kMaxStreams], sin_[kMaxStreams];
-    extern __shared__ float row[];               // [W]: the row the next norm reads
+    extern __shared__ __align__(16) float row[];  // [W]: the row the next norm reads
     const int t = blockIdx.x, W = a.W, S = a.S;
+    const int c_first = threadIdx.x * V, c_step = blockDim.x * V;
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) smix[i] = a.mix ? a.mix[i] : (i / S == i % S ? 1.f : 0.f);
     for (int i = threadIdx.x; i < S; i += blockDim.x) {
         sout[i] = a.out ? a.out[i] : 1.f;
@@ -52,9 +97,18 @@ __global__ void __launch_bounds__(256) hyper_joint_kernel(HyperArgs a) {
     float r0 = 1.f, r1 = 1.f;
     if (a.g0 || a.g1) {                          // branch results that are normed over the width before they are summed
         float q0 = 0.f, q1 = 0.f;
-        for (int c = threadIdx.x; c < W; c += blockDim.x) {
-            if (a.g0) { const float v = a.y0[(size_t)t * W + c]; q0 = fmaf(v, v, q0); }
-            if (a.g1) { const float v = a.y1[(size_t)t * W + c]; q1 = fmaf(v, v, q1); }
+        for (int c = c_first; c < W; c += c_step) {
+            float v[V];
+            if (a.g0) {
+                ld_cols<V>(v, a.y0 + (size_t)t * W + c);
+#pragma unroll
+                for (int i = 0; i < V; ++i) q0 = fmaf(v[i], v[i], q0);
+            }
+            if (a.g1) {
+                ld_cols<V>(v, a.y1 + (size_t)t * W + c);
+#pragma unroll
+                for (int i = 0; i < V; ++i) q1 = fmaf(v[i], v[i], q1);
+            }
         }
         if (a.g0) r0 = 1.f / sqrtf(cta_total(q0, red) / (float)W + a.eps);
         if (a.g1) r1 = 1.f / sqrtf(cta_total(q1, red) / (float)W + a.eps);
@@ -64,63 +118,120 @@ __global__ void __launch_bounds__(256) hyper_joint_kernel(HyperArgs a) {
     float total = 0.f;
     if (a.tokens) {
         const __nv_bfloat16* er = (const __nv_bfloat16*)a.embed + (size_t)a.tokens[t] * W;
-        for (int c = threadIdx.x; c < W; c += blockDim.x) {
-            const float x = __bfloat162float(er[c]) * a.embed_scale;
-            for (int s = 0; s < S; ++s) X[(size_t)s * W + c] = x;
-            float u = 0.f;
-            for (int s = 0; s < S; ++s) u = fmaf(sin_[s], x, u);
-            row[c] = u;
-            total += u;
-            if (a.sum_out) a.sum_out[(size_t)t * W + c] = x * (float)S;
+        for (int c = c_first; c < W; c += c_step) {
+            float x[V], u[V], sm[V];
+            ld_cols_bf16<V>(x, er + c);
+#pragma unroll
+            for (int i = 0; i < V; ++i) x[i] *= a.embed_scale;
+            for (int s = 0; s < S; ++s) st_cols<V>(X + (size_t)s * W + c, x);
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                float ui = 0.f;
+                for (int s = 0; s < S; ++s) ui = fmaf(sin_[s], x[i], ui);
+                u[i] = ui;
+                total += ui;
+                sm[i] = x[i] * (float)S;
+            }
+            st_cols<V>(row + c, u);
+            if (a.sum_out) st_cols<V>(a.sum_out + (size_t)t * W + c, sm);
         }
     } else {
-        for (int c = threadIdx.x; c < W; c += blockDim.x) {
-            float y = 0.f;
-            if (a.y0) y = a.s0 * (a.g0 ? a.y0[(size_t)t * W + c] * r0 * a.g0[c] : a.y0[(size_t)t * W + c]);
-            if (a.y1) y = fmaf(a.s1, a.g1 ? a.y1[(size_t)t * W + c] * r1 * a.g1[c] : a.y1[(size_t)t * W + c], y);
-            for (int k = 0; k < a.top; ++k) {
-                const float e = a.eout[(size_t)a.slot_pos[(size_t)t * a.top + k] * W + c];
-                y = a.wt ? fmaf(a.wt[(size_t)t * a.top + k], e, y) : y + e;
-            }
-            float xs[MS];
+        for (int c = c_first; c < W; c += c_step) {
+            float y[V], g[V], v[V];
 #pragma unroll
-            for (int s = 0; s < MS; ++s) xs[s] = s < S ? X[(size_t)s * W + c] : 0.f;
-            float u = 0.f, sum = 0.f;
+            for (int i = 0; i < V; ++i) y[i] = 0.f;
+            if (a.y0) {
+                ld_cols<V>(v, a.y0 + (size_t)t * W + c);
+                if (a.g0) {
+                    ld_cols<V>(g, a.g0 + c);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] = v[i] * r0 * g[i];
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = a.s0 * v[i];
+            }
+            if (a.y1) {
+                ld_cols<V>(v, a.y1 + (size_t)t * W + c);
+                if (a.g1) {
+                    ld_cols<V>(g, a.g1 + c);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] = v[i] * r1 * g[i];
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = fmaf(a.s1, v[i], y[i]);
+            }
+            for (int k = 0; k < a.top; ++k) {
+                ld_cols<V>(v, a.eout + (size_t)a.slot_pos[(size_t)t * a.top + k] * W + c);
+                const float wk = a.wt ? a.wt[(size_t)t * a.top + k] : 1.f;
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = a.wt ? fmaf(wk, v[i], y[i]) : y[i] + v[i];
+            }
+            float xs[MS][V];
+#pragma unroll
+            for (int s = 0; s < MS; ++s) {
+                if (s < S) {
+                    ld_cols<V>(xs[s], X + (size_t)s * W + c);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) xs[s][i] = 0.f;
+                }
+            }
+            float u[V], sum[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) u[i] = sum[i] = 0.f;
 #pragma unroll
             for (int to = 0; to < MS; ++to) {
                 if (to < S) {
-                    float v = 0.f;
+                    float nv[V];
+#pragma unroll
+                    for (int i = 0; i < V; ++i) nv[i] = 0.f;
 #pragma unroll
                     for (int s = 0; s < MS; ++s)
-                        if (s < S) v = fmaf(smix[s * S + to], xs[s], v);
-                    v = fmaf(sout[to], y, v);
-                    X[(size_t)to * W + c] = v;
-                    u = fmaf(sin_[to], v, u);
-                    sum += v;
+                        if (s < S) {
+                            const float m = smix[s * S + to];
+#pragma unroll
+                            for (int i = 0; i < V; ++i) nv[i] = fmaf(m, xs[s][i], nv[i]);
+                        }
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        nv[i] = fmaf(sout[to], y[i], nv[i]);
+                        u[i] = fmaf(sin_[to], nv[i], u[i]);
+                        sum[i] += nv[i];
+                    }
+                    st_cols<V>(X + (size_t)to * W + c, nv);
                 }
             }
-            row[c] = u;
-            total += u;
-            if (a.sum_out) a.sum_out[(size_t)t * W + c] = sum;
+#pragma unroll
+            for (int i = 0; i < V; ++i) total += u[i];
+            st_cols<V>(row + c, u);
+            if (a.sum_out) st_cols<V>(a.sum_out + (size_t)t * W + c, sum);
         }
     }
     if (!a.hn) return;
     const float mean = cta_total(total, red) / (float)W;
     float dev = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float d = row[c] - mean;
-        dev = fmaf(d, d, dev);
+    for (int c = c_first; c < W; c += c_step) {
+        float u[V];
+        ld_cols<V>(u, row + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float d = u[i] - mean;
+            dev = fmaf(d, d, dev);
+        }
     }
     const float rstd = 1.f / sqrtf(cta_total(dev, red) / (float)W + a.eps);
     __nv_bfloat16 *hi = (__nv_bfloat16*)a.hi, *lo = (__nv_bfloat16*)a.lo;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = (row[c] - mean) * rstd * a.nw[c] + (a.nb ? a.nb[c] : 0.f);
-        a.hn[(size_t)t * W + c] = v;
-        if (hi) {
-            const __nv_bfloat16 h = __float2bfloat16_rn(v);
-            hi[(size_t)t * W + c] = h;
-            lo[(size_t)t * W + c] = __float2bfloat16_rn(v - __bfloat162float(h));
-        }
+    for (int c = c_first; c < W; c += c_step) {
+        float u[V], w[V], b[V];
+        ld_cols<V>(u, row + c);
+        ld_cols<V>(w, a.nw + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) b[i] = 0.f;
+        if (a.nb) ld_cols<V>(b, a.nb + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i) u[i] = (u[i] - mean) * rstd * w[i] + b[i];
+        st_cols<V>(a.hn + (size_t)t * W + c, u);
+        if (hi) st_planes<V>(hi + (size_t)t * W + c, lo + (size_t)t * W + c, u);
     }
 }
 
@@ -314,9 +425,20 @@ int launch_hyper_joint(const HyperArgs& a, int T, cudaStream_t stream) {
     FT_REQUIRE((!a.g0 || a.y0) && (!a.g1 || a.y1) && (a.top == 0 || (a.eout && a.slot_pos)) && (!a.hn || a.nw),
                "hyper joint: missing operands");
     const size_t smem = (size_t)a.W * 4;
-    if (a.S <= 4) hyper_joint_kernel<4><<<T, 256, smem, stream>>>(a);
-    else if (a.S <= 8) hyper_joint_kernel<8><<<T, 256, smem, stream>>>(a);
-    else hyper_joint_kernel<kMaxStreams><<<T, 256, smem, stream>>>(a);
+    // four columns per thread when every row of every operand starts on 16 bytes (bf16 rows on 8): the width decides it for
+    // buffers of the engine's own allocation, so a model always takes the same path
+    auto al = [](const void* p, size_t n) { return ((uintptr_t)p & (n - 1)) == 0; };
+    const bool v4 = a.W % 4 == 0 && al(a.X, 16) && al(a.y0, 16) && al(a.y1, 16) && al(a.g0, 16) && al(a.g1, 16) && al(a.eout, 16) &&
+                    al(a.nw, 16) && al(a.nb, 16) && al(a.hn, 16) && al(a.sum_out, 16) && al(a.embed, 8) && al(a.hi, 8) && al(a.lo, 8);
+    if (v4) {
+        if (a.S <= 4) hyper_joint_kernel<4, 4><<<T, 256, smem, stream>>>(a);
+        else if (a.S <= 8) hyper_joint_kernel<8, 4><<<T, 256, smem, stream>>>(a);
+        else hyper_joint_kernel<kMaxStreams, 1><<<T, 256, smem, stream>>>(a);
+    } else {
+        if (a.S <= 4) hyper_joint_kernel<4, 1><<<T, 256, smem, stream>>>(a);
+        else if (a.S <= 8) hyper_joint_kernel<8, 1><<<T, 256, smem, stream>>>(a);
+        else hyper_joint_kernel<kMaxStreams, 1><<<T, 256, smem, stream>>>(a);
+    }
     FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
