@@ -157,13 +157,13 @@ def test_whole_prompt_matches_oracle(layers):
         eng.close()
 
 
-@pytest.mark.parametrize("streams", [0, 1, 2, 7])
-def test_other_sizes_and_stream_counts(streams):
+@pytest.mark.parametrize("streams,width", [(0, 70), (1, 70), (2, 70), (7, 70), (7, 72), (9, 72)])
+def test_other_sizes_and_stream_counts(streams, width):
     layers = [layer(attention(heads=10, kv_heads=5, dim=12, vdim=14, size=33, scale=0.5, rot=4, base=77.0), moe(ff=10, experts=7, top=4)),
               layer(parallel(left_side(heads=3, kv_heads=3, dim=10, vdim=6, size=8, rot=10, conv=4), inner=33, state=5, dt_rank=3, conv=5)),
               layer(delta(heads=9, kv_heads=3, dim=6, vdim=14, conv=5), dense(ff=50)),
               layer(attention(heads=10, kv_heads=5, dim=12, vdim=14, size=5, scale=0.5, rot=4, base=77.0, kv_from=0))]
-    spec, w = make(layers, width=70, vocab=333, eps=1e-6, seed=9, streams=streams, embed_scale=1.0)
+    spec, w = make(layers, width=width, vocab=333, eps=1e-6, seed=9, streams=streams, embed_scale=1.0)
     eng = engine(spec, w)
     try:
         toks = tokens_of(spec, 90, 2)
