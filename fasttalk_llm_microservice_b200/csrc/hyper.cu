@@ -274,8 +274,17 @@ constexpr int kScanThreads = 128, kScanKeep = 8, kScanChunk = 16, kScanSeg = 128
 __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
 }
-template <int PHASE>
-__global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArgs a, int lpc, int seg_len) {
+// 2^x for x <= 0 in one instruction (results below the normal range become zero)
+__device__ __forceinline__ float ex2_h(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// LPC and KEEP (lanes per channel, states a lane keeps) are fixed at compile time: the loops over a lane's states unroll
+// without guards beyond n < N and the shared-memory reads of a token get constant offsets.
+template <int PHASE, int LPC, int KEEP>
+__global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArgs a, int seg_len) {
+    constexpr int lpc = LPC;
     extern __shared__ __align__(16) float ssm[];
     const int r = blockIdx.y, seg = blockIdx.z + PHASE;
     const int start = a.req_start[r], n_req_tok = a.req_start[r + 1] - start;
@@ -293,9 +302,9 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
     const int stage_f = kScanChunk * (3 * per + 2 * N);
     float* Sg = a.state + (size_t)a.req_slot[r] * a.slot_stride + a.s_off + (size_t)cc * N;
     float* Lw = a.ws + (size_t)a.ws_rows * a.channels * N;    // behind the L rows: the segments' summed step sizes
-    float S[kScanKeep], A[kScanKeep];
+    float S[KEEP], A[KEEP];
 #pragma unroll
-    for (int i = 0; i < kScanKeep; ++i) {
+    for (int i = 0; i < KEEP; ++i) {
         const int n = s + lpc * i;
         A[i] = n < N ? -expf(a.a_log[(size_t)cc * N + n]) * 1.4426950408889634f : 0.f;
         S[i] = 0.f;
@@ -303,7 +312,7 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
     if (seg == 0) {
         if (a.req_pos0[r] != 0) {
 #pragma unroll
-            for (int i = 0; i < kScanKeep; ++i) {
+            for (int i = 0; i < KEEP; ++i) {
                 const int n = s + lpc * i;
                 if (n < N) S[i] = Sg[n];
             }
@@ -311,7 +320,7 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
     } else if (PHASE == 1) {
         const size_t q0 = (size_t)(start / seg_len);         // segment 0's row; the later full segments follow it in order
 #pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) {
+        for (int i = 0; i < KEEP; ++i) {
             const int n = s + lpc * i;
             if (n < N) S[i] = a.ws[(q0 * a.channels + cc) * N + n];
         }
@@ -319,9 +328,9 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
             const size_t q = (size_t)((start + p * seg_len) / seg_len);
             const float d = Lw[q * a.channels + cc];
 #pragma unroll
-            for (int i = 0; i < kScanKeep; ++i) {
+            for (int i = 0; i < KEEP; ++i) {
                 const int n = s + lpc * i;
-                if (n < N) S[i] = fmaf(exp2f(d * A[i]), S[i], a.ws[(q * a.channels + cc) * N + n]);
+                if (n < N) S[i] = fmaf(ex2_h(d * A[i]), S[i], a.ws[(q * a.channels + cc) * N + n]);
             }
         }
     }
@@ -363,15 +372,19 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
             dsum += dt;
             float y = 0.f;
 #pragma unroll
-            for (int i = 0; i < kScanKeep; ++i) {
+            for (int i = 0; i < KEEP; ++i) {
+                // no branch (all lanes of the warp reach the shuffles below together): a lane's states beyond N have A = 0
+                // and read B = C = 0, so they stay zero and add nothing
                 const int n = s + lpc * i;
-                if (n < N) {
-                    S[i] = fmaf(exp2f(dt * A[i]), S[i], dx * sB[k * N + n]);
-                    if (emit) y = fmaf(S[i], sC[k * N + n], y);
-                }
+                const bool has = n < N;
+                const float bn = has ? sB[k * N + (has ? n : 0)] : 0.f;
+                S[i] = fmaf(ex2_h(dt * A[i]), S[i], dx * bn);
+                if (emit) y = fmaf(S[i], has ? sC[k * N + (has ? n : 0)] : 0.f, y);
             }
-            if (emit)
+            if (emit) {
+#pragma unroll
                 for (int off = 1; off < lpc; off <<= 1) y += __shfl_xor_sync(0xffffffffu, y, off);
+            }
             return y;
         };
         if (nt == kScanChunk) {                              // a whole chunk: four tokens at a time with their read-outs in
@@ -402,14 +415,14 @@ __global__ void __launch_bounds__(kScanThreads, 4) selective_scan_kernel(ScanArg
     if (!live) return;
     if (last) {
 #pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) {
+        for (int i = 0; i < KEEP; ++i) {
             const int n = s + lpc * i;
             if (n < N) Sg[n] = S[i];
         }
     } else if (PHASE == 0) {
         const size_t q = (size_t)(seg_start / seg_len);
 #pragma unroll
-        for (int i = 0; i < kScanKeep; ++i) {
+        for (int i = 0; i < KEEP; ++i) {
             const int n = s + lpc * i;
             if (n < N) a.ws[(q * a.channels + c) * N + n] = S[i];
         }
@@ -470,17 +483,35 @@ int launch_selective_scan(const ScanArgs& a, int n_req, cudaStream_t stream) {
     while (lpc * kScanKeep < a.N) lpc <<= 1;
     const int per = kScanThreads / lpc;
     const size_t smem = (size_t)2 * kScanChunk * (3 * per + 2 * a.N) * 4;
-    if (smem > 48 * 1024) {
-        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
     const unsigned cx = (a.channels + per - 1) / per;
-    selective_scan_kernel<0><<<dim3(cx, n_req, std::max(1, n_seg - 1)), kScanThreads, smem, stream>>>(a, lpc, seg_len);
-    FT_CHECK_CUDA(cudaGetLastError());
-    if (n_seg > 1) {
-        selective_scan_kernel<1><<<dim3(cx, n_req, n_seg - 1), kScanThreads, smem, stream>>>(a, lpc, seg_len);
-        FT_CHECK_CUDA(cudaGetLastError());
+    const int need = (a.N + lpc - 1) / lpc, keep = need <= 2 ? 2 : need <= 4 ? 4 : kScanKeep;
+    const dim3 g0(cx, n_req, std::max(1, n_seg - 1)), g1(cx, n_req, std::max(1, n_seg - 1));
+#define FT_SCAN_ONE(L, K)                                                                                             \
+    do {                                                                                                              \
+        if (smem > 48 * 1024) {                                                                                       \
+            FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<0, L, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            FT_CHECK_CUDA(cudaFuncSetAttribute(selective_scan_kernel<1, L, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        }                                                                                                             \
+        selective_scan_kernel<0, L, K><<<g0, kScanThreads, smem, stream>>>(a, seg_len);                               \
+        if (n_seg > 1) selective_scan_kernel<1, L, K><<<g1, kScanThreads, smem, stream>>>(a, seg_len);                \
+    } while (0)
+#define FT_SCAN(L)                                \
+    do {                                          \
+        if (keep == 2) FT_SCAN_ONE(L, 2);         \
+        else if (keep == 4) FT_SCAN_ONE(L, 4);    \
+        else FT_SCAN_ONE(L, 8);                   \
+    } while (0)
+    switch (lpc) {
+        case 1: FT_SCAN(1); break;
+        case 2: FT_SCAN(2); break;
+        case 4: FT_SCAN(4); break;
+        case 8: FT_SCAN(8); break;
+        case 16: FT_SCAN(16); break;
+        default: FT_SCAN(32); break;
     }
+#undef FT_SCAN
+#undef FT_SCAN_ONE
+    FT_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
 
